@@ -69,8 +69,9 @@ def cmd_inspect(args) -> int:
     from .config import load_config, get_architecture
     from .weights import read_model_tensors, check_tensors
     cfg = load_config(args.model)
-    spec = get_architecture(cfg.architecture).build_spec(cfg)
     tensors = read_model_tensors(args.model)
+    cfg.sizes_from_tensors({name: tuple(t.shape) for name, t in tensors.items()})
+    spec = get_architecture(cfg.architecture).build_spec(cfg)
     n = sum(t.numel() for t in tensors.values())
     print(f"{cfg.architecture}: {len(spec.layers)} layers, width {spec.width}, vocabulary {spec.vocab_size}, "
           f"{len(tensors)} tensors, {n} parameters")

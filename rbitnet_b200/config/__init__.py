@@ -2,9 +2,10 @@ from .base import ModelConfig, ConfigError, read_config_json
 from .llama import LlamaConfig
 from .safuvik import SafuvikConfig
 from .vaderax import VaderaxConfig
+from .nifarax import NifaraxConfig
 from .registry import (register_architecture, unregister_architecture, known_architectures,
                        get_architecture, architecture_of, config_from_dict, load_config)
 
-__all__ = ["ModelConfig", "ConfigError", "read_config_json", "LlamaConfig", "SafuvikConfig", "VaderaxConfig",
+__all__ = ["ModelConfig", "ConfigError", "read_config_json", "LlamaConfig", "SafuvikConfig", "VaderaxConfig", "NifaraxConfig",
            "register_architecture", "unregister_architecture", "known_architectures",
            "get_architecture", "architecture_of", "config_from_dict", "load_config"]

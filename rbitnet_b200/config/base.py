@@ -52,6 +52,11 @@ class ModelConfig:
     def validate(self) -> None:  # pragma: no cover - overridden
         pass
 
+    def sizes_from_tensors(self, shapes: Mapping[str, tuple]) -> None:
+        """Called with the shapes of a model's tensors (name -> shape) before the model is built from this
+        configuration: a design in which a size is given by a tensor's shape rather than by a config.json key takes
+        it here.  Most designs name every size, and do nothing."""
+
     def to_dict(self) -> dict:
         d = asdict(self)
         d["architectures"] = [self.architecture]

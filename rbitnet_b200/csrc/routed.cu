@@ -8,6 +8,10 @@
 //   outputs n_experts .. n-1 are identity experts: their result is the input row itself
 //   result_t = sum over the chosen e of s_e * expert_e(h_t)
 //
+// Variants, each a parameter: `scoring` 1 takes s = sigmoid(z), output by output, instead of the softmax; the router's
+// matrix may hold `n_extra` further rows after the n outputs, whose sums leave as they are (a gate that reads the same
+// rows); the gather may multiply a pair's input row by the pair's weight (experts whose weight acts on the input).
+//
 // The pairs whose expert has weights are sorted by expert into rows of a padded buffer in which every
 // expert's rows start on a tile border, so that a tile of rows multiplies by one expert's matrix
 // (tile_group[tile]: the expert, or -1 for a tile without rows).  Where a pair lands inside its
@@ -38,7 +42,15 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
 // its `top` outputs and their weights.
 __device__ __forceinline__ void route_select(float* z, float* choice, float* gscore, const float* __restrict__ correction,
                                              int n, int top, int groups, int keep, int lane, int* __restrict__ ids,
-                                             float* __restrict__ weights, int64_t t) {
+                                             float* __restrict__ weights, int64_t t, int scoring = 0) {
+  if (scoring == 1) {
+    for (int e = lane; e < n; e += 32) {
+      const float s = 1.0f / (1.0f + expf(-z[e]));
+      z[e] = s;
+      choice[e] = s + (correction != nullptr ? correction[e] : 0.f);
+    }
+    __syncwarp();
+  } else {
   float m = -INFINITY;
   for (int e = lane; e < n; e += 32) m = fmaxf(m, z[e]);
   m = rb_warp_max(m);
@@ -53,6 +65,7 @@ __device__ __forceinline__ void route_select(float* z, float* choice, float* gsc
     choice[e] = s + (correction != nullptr ? correction[e] : 0.f);
   }
   __syncwarp();
+  }
   // the largest value of v[0..count) that is not -inf, lowest index on ties; every lane gets the index
   auto arg_max = [&](const float* v, int count) {
     float best = -INFINITY;
@@ -108,10 +121,12 @@ template <typename TI>
 __global__ void __launch_bounds__(256) route_kernel(int* __restrict__ ids, float* __restrict__ weights,
                                                     const TI* __restrict__ h, int64_t ldh,
                                                     const float* __restrict__ Wr, const float* __restrict__ correction,
-                                                    int T, int K, int n, int top, int groups, int keep, int TB, int vec) {
+                                                    int T, int K, int n_out, int top, int groups, int keep, int TB, int vec,
+                                                    int scoring, int n_extra, float* __restrict__ extra) {
   rb_pdl_launch_dependents();
   extern __shared__ float s_route[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = n_out + n_extra;                       // rows of Wr: the outputs, then the extra rows
   const int per_token = 2 * n + 2 * groups;
   const int t0 = blockIdx.x * TB;
   const int nt = min(TB, T - t0);
@@ -180,7 +195,8 @@ __global__ void __launch_bounds__(256) route_kernel(int* __restrict__ ids, float
   __syncthreads();
   if (warp >= nt) return;
   float* z = s_route + (size_t)warp * per_token;     // scores, choice scores, group scores, kept groups
-  route_select(z, z + n, z + 2 * n, correction, n, top, groups, keep, lane, ids, weights, t0 + warp);
+  for (int i = lane; i < n_extra; i += 32) extra[(int64_t)(t0 + warp) * n_extra + i] = z[n_out + i];
+  route_select(z, z + n, z + 2 * n, correction, n_out, top, groups, keep, lane, ids, weights, t0 + warp, scoring);
 }
 
 // Many tokens: the router's sums as a tiled float32 product (16 tokens by 64 outputs a block, k in steps of 32 through
@@ -242,7 +258,8 @@ __global__ void __launch_bounds__(256) route_logits_kernel(float* __restrict__ z
 
 __global__ void __launch_bounds__(128) route_select_kernel(int* __restrict__ ids, float* __restrict__ weights,
                                                            const float* __restrict__ zg, const float* __restrict__ correction,
-                                                           int T, int n, int top, int groups, int keep) {
+                                                           int T, int n, int top, int groups, int keep, int scoring,
+                                                           int n_extra, float* __restrict__ extra) {
   rb_pdl_launch_dependents();
   extern __shared__ float s_route[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -250,9 +267,11 @@ __global__ void __launch_bounds__(128) route_select_kernel(int* __restrict__ ids
   float* z = s_route + (size_t)warp * (2 * n + 2 * groups);
   rb_pdl_wait();
   if (t >= T) return;
-  for (int e = lane; e < n; e += 32) z[e] = zg[(int64_t)t * n + e];
+  const int64_t ldz = n + n_extra;                     // zg holds the outputs' sums, then the extra rows'
+  for (int e = lane; e < n; e += 32) z[e] = zg[(int64_t)t * ldz + e];
+  for (int i = lane; i < n_extra; i += 32) extra[(int64_t)t * n_extra + i] = zg[(int64_t)t * ldz + n + i];
   __syncwarp();
-  route_select(z, z + n, z + 2 * n, correction, n, top, groups, keep, lane, ids, weights, t);
+  route_select(z, z + n, z + 2 * n, correction, n, top, groups, keep, lane, ids, weights, t, scoring);
 }
 
 // ---------------------------------------------------------------- plan
@@ -330,6 +349,27 @@ __global__ void gather_kernel(T* __restrict__ xp, const T* __restrict__ h, int64
   for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = src[k];
 }
 
+// xp[r, :] = w * h[row_token[r], :] with w the weight of the pair that owns row r (the token's choice j with
+// pos[token, j] == r), rounded to the rows' type; zeros for padding rows.
+template <typename T>
+__global__ void gather_scaled_kernel(T* __restrict__ xp, const T* __restrict__ h, int64_t ldh, const int* __restrict__ row_token,
+                                     const int* __restrict__ pos, const float* __restrict__ weights, int top, int K) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int r = blockIdx.x;
+  const int t = row_token[r];
+  T* dst = xp + (int64_t)r * K;
+  if (t < 0) {
+    for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = rb_from_float<T>(0.f);
+    return;
+  }
+  float w = 0.f;
+  for (int j = 0; j < top; ++j)
+    if (pos[(int64_t)t * top + j] == r) w = weights[(int64_t)t * top + j];
+  const T* src = h + (int64_t)t * ldh;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = rb_from_float<T>(w * rb_to_float<T>(src[k]));
+}
+
 // ---------------------------------------------------------------- weighted sum
 // x[t, :] (+)= sum_j w[t, j] * (pos[t, j] >= 0 ? y[pos[t, j], :] : h[t, :]), the choices in their order.
 template <typename T>
@@ -345,7 +385,7 @@ __global__ void combine_kernel(float* __restrict__ x, int64_t ldx, const float* 
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       for (int j = 0; j < top; ++j) {
         const int r = pos[(int64_t)t * top + j];
-        const float w = weights[(int64_t)t * top + j];
+        const float w = weights != nullptr ? weights[(int64_t)t * top + j] : 1.0f;
         float v[4];
         if (r >= 0) load4(y + (int64_t)r * E + c, v);
         else load4(h + (int64_t)t * ldh + c, v);
@@ -366,7 +406,7 @@ __global__ void combine_kernel(float* __restrict__ x, int64_t ldx, const float* 
     float acc = 0.f;
     for (int j = 0; j < top; ++j) {
       const int r = pos[(int64_t)t * top + j];
-      const float w = weights[(int64_t)t * top + j];
+      const float w = weights != nullptr ? weights[(int64_t)t * top + j] : 1.0f;
       const float v = r >= 0 ? y[(int64_t)r * E + c] : rb_to_float<T>(h[(int64_t)t * ldh + c]);
       acc = fmaf(w, v, acc);
     }
@@ -453,10 +493,13 @@ __global__ void square_relu_kernel(T* __restrict__ out, const T* __restrict__ in
 // ids, weights: [T, top].  h: the input rows (dtype h_dtype).  Wr: float32 [n, K]; correction: float32 [n] or null.
 // groups <= 1 or keep >= groups: every output can be chosen.  z_scratch: T * n floats (from 64 tokens on, the router's
 // sums are a product of their own that leaves them there), or null.
-RB_EXPORT int rb_route(int* ids, float* weights, const void* h, int64_t ldh, int h_dtype, const float* Wr,
-                       const float* correction, int T, int K, int n, int top, int groups, int keep, float* z_scratch,
-                       cudaStream_t stream) {
+static int route_impl(int* ids, float* weights, const void* h, int64_t ldh, int h_dtype, const float* Wr,
+                      const float* correction, int T, int K, int n, int top, int groups, int keep, float* z_scratch,
+                      int scoring, int n_extra, float* extra, cudaStream_t stream) {
   if (T == 0) return 0;
+  RB_REQUIRE(scoring == 0 || scoring == 1, "rb_route: scoring %d is not built (0: softmax, 1: sigmoid)", scoring);
+  RB_REQUIRE(n_extra >= 0 && (n_extra == 0 || extra != nullptr), "rb_route: %d extra rows and nowhere to leave them", n_extra);
+  const int n_all = n + n_extra;
   RB_REQUIRE(K > 0 && n > 0 && top > 0 && top <= n, "rb_route: bad sizes K=%d outputs=%d top=%d", K, n, top);
   RB_REQUIRE(groups <= 1 || n % groups == 0, "rb_route: %d outputs are not %d equal groups", n, groups);
   if (groups < 1) groups = 1;
@@ -466,31 +509,46 @@ RB_EXPORT int rb_route(int* ids, float* weights, const void* h, int64_t ldh, int
     RB_REQUIRE(smem_sel <= 48 * 1024, "rb_route: %d router outputs are more than a block's shared memory holds", n);
     const int blocks_l = (T + RL_TM - 1) / RL_TM;
     if (h_dtype == RB_F32)
-      RB_LAUNCH("route_logits_kernel", (route_logits_kernel<float>), blocks_l, 256, 0, stream, z_scratch, (const float*)h, ldh, Wr, T, K, n);
+      RB_LAUNCH("route_logits_kernel", (route_logits_kernel<float>), blocks_l, 256, 0, stream, z_scratch, (const float*)h, ldh, Wr, T, K, n_all);
     else if (h_dtype == RB_BF16)
-      RB_LAUNCH("route_logits_kernel", (route_logits_kernel<__nv_bfloat16>), blocks_l, 256, 0, stream, z_scratch, (const __nv_bfloat16*)h, ldh, Wr, T, K, n);
+      RB_LAUNCH("route_logits_kernel", (route_logits_kernel<__nv_bfloat16>), blocks_l, 256, 0, stream, z_scratch, (const __nv_bfloat16*)h, ldh, Wr, T, K, n_all);
     else
       RB_FAIL("rb_route: unknown dtype %d", h_dtype);
     RB_CHECK_LAUNCH("rb_route");
     RB_LAUNCH("route_select_kernel", (route_select_kernel), (T + 3) / 4, 128, smem_sel, stream, ids, weights, z_scratch, correction, T, n, top,
-              groups, keep);
+              groups, keep, scoring, n_extra, extra);
     RB_CHECK_LAUNCH("rb_route");
     return 0;
   }
   const int TB = T >= 64 ? ROUTE_TB : 1;
-  const size_t smem = (size_t)TB * (2 * n + 2 * groups) * sizeof(float);
+  const size_t smem = (size_t)TB * (2 * n_all + 2 * groups) * sizeof(float);
   RB_REQUIRE(smem <= 48 * 1024, "rb_route: %d router outputs are more than a block's shared memory holds", n);
   const int blocks = (T + TB - 1) / TB;
   const int elem = h_dtype == RB_F32 ? 4 : 2;
   const int vec = K % 4 == 0 && ldh % 4 == 0 && (uintptr_t)h % (4 * elem) == 0 && (uintptr_t)Wr % 16 == 0;
   if (h_dtype == RB_F32)
-    RB_LAUNCH("route_kernel", (route_kernel<float>), blocks, 256, smem, stream, ids, weights, (const float*)h, ldh, Wr, correction, T, K, n, top, groups, keep, TB, vec);
+    RB_LAUNCH("route_kernel", (route_kernel<float>), blocks, 256, smem, stream, ids, weights, (const float*)h, ldh, Wr, correction, T, K, n, top, groups, keep, TB, vec, scoring, n_extra, extra);
   else if (h_dtype == RB_BF16)
-    RB_LAUNCH("route_kernel", (route_kernel<__nv_bfloat16>), blocks, 256, smem, stream, ids, weights, (const __nv_bfloat16*)h, ldh, Wr, correction, T, K, n, top, groups, keep, TB, vec);
+    RB_LAUNCH("route_kernel", (route_kernel<__nv_bfloat16>), blocks, 256, smem, stream, ids, weights, (const __nv_bfloat16*)h, ldh, Wr, correction, T, K, n, top, groups, keep, TB, vec, scoring, n_extra, extra);
   else
     RB_FAIL("rb_route: unknown dtype %d", h_dtype);
   RB_CHECK_LAUNCH("rb_route");
   return 0;
+}
+
+RB_EXPORT int rb_route(int* ids, float* weights, const void* h, int64_t ldh, int h_dtype, const float* Wr,
+                       const float* correction, int T, int K, int n, int top, int groups, int keep, float* z_scratch,
+                       cudaStream_t stream) {
+  return route_impl(ids, weights, h, ldh, h_dtype, Wr, correction, T, K, n, top, groups, keep, z_scratch, 0, 0, nullptr, stream);
+}
+
+// The same with the variants: scoring (0: softmax over the outputs, 1: a sigmoid per output); Wr holds n + n_extra rows
+// and the sums of the last n_extra leave in extra [T, n_extra]; z_scratch then holds T * (n + n_extra) floats.
+RB_EXPORT int rb_route_scored(int* ids, float* weights, const void* h, int64_t ldh, int h_dtype, const float* Wr,
+                              const float* correction, int T, int K, int n, int top, int groups, int keep, float* z_scratch,
+                              int scoring, int n_extra, float* extra, cudaStream_t stream) {
+  return route_impl(ids, weights, h, ldh, h_dtype, Wr, correction, T, K, n, top, groups, keep, z_scratch, scoring, n_extra, extra,
+                    stream);
 }
 
 // The choice alone, from router sums z [T, n] that a product has left (float32).
@@ -503,7 +561,7 @@ RB_EXPORT int rb_route_select(int* ids, float* weights, const float* z, const fl
   const size_t smem_sel = (size_t)4 * (2 * n + 2 * groups) * sizeof(float);
   RB_REQUIRE(smem_sel <= 48 * 1024, "rb_route_select: %d router outputs are more than a block's shared memory holds", n);
   RB_LAUNCH("route_select_kernel", (route_select_kernel), (T + 3) / 4, 128, smem_sel, stream, ids, weights, z, correction, T, n, top,
-            groups, keep);
+            groups, keep, 0, 0, (float*)nullptr);
   RB_CHECK_LAUNCH("rb_route_select");
   return 0;
 }
@@ -538,6 +596,21 @@ RB_EXPORT int rb_routed_gather(void* xp, const void* h, int64_t ldh, int dtype, 
   else
     RB_FAIL("rb_routed_gather: unknown dtype %d", dtype);
   RB_CHECK_LAUNCH("rb_routed_gather");
+  return 0;
+}
+
+// The gather with every row multiplied by its pair's weight (pos, weights: [T, top] as the plan and the router left them).
+RB_EXPORT int rb_routed_gather_scaled(void* xp, const void* h, int64_t ldh, int dtype, const int* row_token, const int* pos,
+                                      const float* weights, int top, int rows, int K, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  const int threads = K >= 256 ? 256 : (K >= 128 ? 128 : 64);
+  if (dtype == RB_F32)
+    RB_LAUNCH("gather_scaled_kernel", (gather_scaled_kernel<float>), rows, threads, 0, stream, (float*)xp, (const float*)h, ldh, row_token, pos, weights, top, K);
+  else if (dtype == RB_BF16)
+    RB_LAUNCH("gather_scaled_kernel", (gather_scaled_kernel<__nv_bfloat16>), rows, threads, 0, stream, (__nv_bfloat16*)xp, (const __nv_bfloat16*)h, ldh, row_token, pos, weights, top, K);
+  else
+    RB_FAIL("rb_routed_gather_scaled: unknown dtype %d", dtype);
+  RB_CHECK_LAUNCH("rb_routed_gather_scaled");
   return 0;
 }
 

@@ -1,0 +1,179 @@
+// What stands around a sublayer in a block with filtered inputs and gated results:
+//
+//   grouped RMS norm   a row cut into `groups` equal consecutive parts, each divided by sqrt(mean(part^2) + eps),
+//                      the whole multiplied by w
+//   input filter       h_t + sum_j taps[:, j] h_(t - K + 1 + j) over time on every channel (causal, zeros before a
+//                      sequence's start); the last K - 1 inputs of a sequence live in a ring of K rows by position
+//   gated residual     x += y * sigmoid(g + b), value by value
+//   scaled rows        y += sigmoid(logit_t) * z, one number per row
+//   soft cap           v <- cap * tanh(v / cap)
+//
+// All arithmetic is float32; rows enter and leave in the compute dtype where they feed a product.
+#include "rb_common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float sigmoid_(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+// ---------------------------------------------------------------- grouped RMS norm
+// A block per row; a warp takes the row's parts in turn (two passes over the part: the sum of squares, then the
+// values; the second pass finds the part in the SM's cache).
+template <typename TO>
+__global__ void __launch_bounds__(256) rmsnorm_grouped_kernel(TO* __restrict__ out, const float* __restrict__ x,
+                                                              const float* __restrict__ w, int E, int groups, float eps) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int per = E / groups;
+  const float* row = x + (int64_t)blockIdx.x * E;
+  TO* dst = out + (int64_t)blockIdx.x * E;
+  for (int g = warp; g < groups; g += nw) {
+    const float* p = row + (int64_t)g * per;
+    float ss = 0.f;
+    for (int i = lane; i < per; i += 32) ss = fmaf(p[i], p[i], ss);
+    ss = rb_warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)per + eps);
+    for (int i = lane; i < per; i += 32) dst[(int64_t)g * per + i] = rb_from_float<TO>(p[i] * r * w[g * per + i]);
+  }
+}
+
+// ---------------------------------------------------------------- input filter
+// out[t, c] = h[t, c] + sum_d taps[c, K-1-d] * h(d rows back), rows before the run taken from the ring (zeros before
+// position 0).  With `update` (every row is its own run) the row also goes into the ring at its position: the rows it
+// read lie at other positions of the ring.
+template <typename T>
+__global__ void input_filter_kernel(T* __restrict__ out, const T* __restrict__ h, const float* __restrict__ taps,
+                                    float* __restrict__ ring, const int* __restrict__ tok_first,
+                                    const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, int n_tokens, int C,
+                                    int K, int update, int per_block) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  for (int t = blockIdx.x * per_block; t < min(n_tokens, (int)(blockIdx.x + 1) * per_block); ++t) {
+    const int first = tok_first != nullptr ? tok_first[t] : t;
+    const int slot = tok_slot[t], pos = tok_pos[t];
+    const int j = t - first;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+      const float own = rb_to_float<T>(h[(int64_t)t * C + c]);
+      float acc = own;
+      for (int d = 0; d < K; ++d) {
+        float v;
+        if (d == 0) v = own;
+        else if (d <= j) v = rb_to_float<T>(h[(int64_t)(t - d) * C + c]);
+        else if (pos - d < 0) v = 0.f;
+        else v = ring[((int64_t)slot * K + (pos - d) % K) * C + c];
+        acc = fmaf(taps[(int64_t)c * K + (K - 1 - d)], v, acc);
+      }
+      out[(int64_t)t * C + c] = rb_from_float<T>(acc);
+      if (update && K > 1) ring[((int64_t)slot * K + pos % K) * C + c] = own;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- gated residual
+template <typename TG>
+__global__ void gated_add_kernel(float* __restrict__ x, const float* __restrict__ y, const TG* __restrict__ g, int64_t ldg,
+                                 const float* __restrict__ bias, int64_t n, int E) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / E;
+    const int c = (int)(i - t * E);
+    const float z = rb_to_float<TG>(g[t * ldg + c]) + (bias != nullptr ? bias[c] : 0.f);
+    x[i] = fmaf(y[i], sigmoid_(z), x[i]);
+  }
+}
+
+__global__ void add_scaled_rows_kernel(float* __restrict__ y, const float* __restrict__ z, const float* __restrict__ logit,
+                                       int64_t ldl, int64_t n, int E) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / E;
+    y[i] = fmaf(z[i], sigmoid_(logit[t * ldl]), y[i]);
+  }
+}
+
+__global__ void softcap_kernel(float* __restrict__ v, int64_t n, float cap) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const float inv = 1.0f / cap;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    v[i] = cap * tanhf(v[i] * inv);
+}
+
+inline int flat_blocks(int64_t n, int threads) {
+  const int64_t most = (int64_t)rb_sm_count() * 16;
+  const int64_t want = (n + threads - 1) / threads;
+  return (int)(want < most ? want : most);
+}
+
+}  // namespace
+
+RB_EXPORT int rb_rmsnorm_grouped(void* out, int out_dtype, const float* x, const float* w, int T, int E, int groups,
+                                 float eps, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(groups >= 1 && E > 0 && E % groups == 0, "rb_rmsnorm_grouped: a row of %d values is not %d equal parts", E, groups);
+  const int threads = groups >= 8 ? 256 : 32 * groups;
+  if (out_dtype == RB_F32)
+    RB_LAUNCH("rmsnorm_grouped_kernel", (rmsnorm_grouped_kernel<float>), T, threads, 0, stream, (float*)out, x, w, E, groups, eps);
+  else if (out_dtype == RB_BF16)
+    RB_LAUNCH("rmsnorm_grouped_kernel", (rmsnorm_grouped_kernel<__nv_bfloat16>), T, threads, 0, stream, (__nv_bfloat16*)out, x, w, E, groups, eps);
+  else
+    RB_FAIL("rb_rmsnorm_grouped: unknown dtype %d", out_dtype);
+  RB_CHECK_LAUNCH("rb_rmsnorm_grouped");
+  return 0;
+}
+
+// h, out: [T, C] in `dtype`; taps: float32 [C, K]; ring: float32 [n_slots, K, C].  tok_first: per row the first row of
+// its run, or null when every row is its own run (the ring is then moved on here; else rb_conv_tail_update does it).
+RB_EXPORT int rb_input_filter(void* out, const void* h, int dtype, const float* taps, float* ring, const int* tok_first,
+                              const int* tok_slot, const int* tok_pos, int T, int C, int K, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(C > 0 && K >= 1, "rb_input_filter: bad sizes C=%d K=%d", C, K);
+  const int threads = 128;
+  int by = (C + threads - 1) / threads;
+  if (by > 64) by = 64;
+  const int per_block = T >= 512 ? 8 : 1;
+  const dim3 grid((T + per_block - 1) / per_block, by);
+  const int update = tok_first == nullptr ? 1 : 0;
+  if (dtype == RB_F32)
+    RB_LAUNCH("input_filter_kernel", (input_filter_kernel<float>), grid, threads, 0, stream, (float*)out, (const float*)h, taps, ring, tok_first, tok_slot, tok_pos, T, C, K, update, per_block);
+  else if (dtype == RB_BF16)
+    RB_LAUNCH("input_filter_kernel", (input_filter_kernel<__nv_bfloat16>), grid, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)h, taps, ring, tok_first, tok_slot, tok_pos, T, C, K, update, per_block);
+  else
+    RB_FAIL("rb_input_filter: unknown dtype %d", dtype);
+  RB_CHECK_LAUNCH("rb_input_filter");
+  return 0;
+}
+
+// x [T, E] += y [T, E] * sigmoid(g[t, c] + bias[c]); g has rows of ldg values in g_dtype.
+RB_EXPORT int rb_gated_add(float* x, const float* y, const void* g, int64_t ldg, int g_dtype, const float* bias, int T, int E,
+                           cudaStream_t stream) {
+  if (T == 0) return 0;
+  const int64_t n = (int64_t)T * E;
+  if (g_dtype == RB_F32)
+    RB_LAUNCH("gated_add_kernel", (gated_add_kernel<float>), flat_blocks(n, 256), 256, 0, stream, x, y, (const float*)g, ldg, bias, n, E);
+  else if (g_dtype == RB_BF16)
+    RB_LAUNCH("gated_add_kernel", (gated_add_kernel<__nv_bfloat16>), flat_blocks(n, 256), 256, 0, stream, x, y, (const __nv_bfloat16*)g, ldg, bias, n, E);
+  else
+    RB_FAIL("rb_gated_add: unknown dtype %d", g_dtype);
+  RB_CHECK_LAUNCH("rb_gated_add");
+  return 0;
+}
+
+// y [T, E] += sigmoid(logit[t * ldl]) * z [T, E]
+RB_EXPORT int rb_add_scaled_rows(float* y, const float* z, const float* logit, int64_t ldl, int T, int E, cudaStream_t stream) {
+  if (T == 0) return 0;
+  const int64_t n = (int64_t)T * E;
+  RB_LAUNCH("add_scaled_rows_kernel", (add_scaled_rows_kernel), flat_blocks(n, 256), 256, 0, stream, y, z, logit, ldl, n, E);
+  RB_CHECK_LAUNCH("rb_add_scaled_rows");
+  return 0;
+}
+
+RB_EXPORT int rb_softcap(float* v, long long n, float cap, cudaStream_t stream) {
+  if (n == 0) return 0;
+  RB_REQUIRE(cap > 0.f, "rb_softcap: the cap must be positive");
+  RB_LAUNCH("softcap_kernel", (softcap_kernel), flat_blocks(n, 256), 256, 0, stream, v, (int64_t)n, cap);
+  RB_CHECK_LAUNCH("rb_softcap");
+  return 0;
+}

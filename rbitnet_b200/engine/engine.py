@@ -63,6 +63,7 @@ class Engine:
         self.model_path = model_path
         self.dtype = _dtype(dtype)
         self.ops = ops if ops is not None else CudaOps(self.dtype, device, verbose_build=verbose)
+        config.sizes_from_tensors({name: tuple(t.shape) for name, t in tensors.items()})
         self.spec = get_architecture(config.architecture).build_spec(config)
         self._tensor_names = sorted(tensors)
         self.model = Model(self.spec, tensors, self.ops)

@@ -38,6 +38,11 @@ class Model:
                                  f"{self.residual_streams}")
         self.final_norm = build_part("norm", spec.final_norm)
         self.final_norm.bind({k: tensors[n].to(dev) for k, n in spec.final_norm_names.items()}, ops)
+        self.embedding_norm = None
+        if getattr(spec, "embedding_norm", None) is not None:
+            self.embedding_norm = build_part("norm", spec.embedding_norm)
+            self.embedding_norm.bind({k: tensors[n].to(dev) for k, n in spec.embedding_norm_names.items()}, ops)
+        self.logit_softcap = float(getattr(spec, "logit_softcap", 0.0) or 0.0)
         self.embedding = ops.prepare_embedding(tensors[spec.embedding_name])
         if spec.head_name is None:
             self.head = ops.prepare_linear([self.embedding])     # tied: the table itself
@@ -61,6 +66,7 @@ class Model:
 
     # what the cache has to provide
     def cache_plan(self):
+        from ..parts.base import Mixer
         cache_needs, reads, state_needs = {}, {}, {}
         for e, entry in enumerate(self.spec.schedule):
             mixer = self._mixer_of(self.blocks[entry.layer], entry.layer)
@@ -80,6 +86,15 @@ class Model:
             st = mixer.state_need()
             if st:
                 state_needs[e] = st            # one StateNeed, or several by name
+        # parts of a block other than its mixer that keep state per sequence (an input filter): per run of the layer
+        for e, entry in enumerate(self.spec.schedule):
+            for name, part in self.blocks[entry.layer].parts().items():
+                if isinstance(part, Mixer):
+                    continue
+                need = getattr(part, "state_need", None)
+                st = need() if need is not None else None
+                if st:
+                    state_needs[("part", e, name)] = st
         return cache_needs, reads, state_needs
 
     def weight_bytes(self) -> int:
@@ -119,6 +134,8 @@ class Model:
         """Runs the step's tokens; returns float32 logits [wanted rows, vocab] or None."""
         ops, meta = ctx.ops, ctx.meta
         x = ops.embed(meta.token_ids, self.embedding, self.embedding_scale)   # float32 residual stream [T, E]
+        if self.embedding_norm is not None:
+            x = self.embedding_norm.forward(ctx, x, out_dtype=torch.float32)
         s = self.residual_streams
         if s > 1:
             x = ops.streams_expand(x, s)                                      # [T, s * E]: every stream starts as the embedding
@@ -160,4 +177,7 @@ class Model:
         if s > 1:
             rows = ops.streams_sum(rows, s)
         h = self.final_norm.forward(ctx, rows)
-        return ops.linear(h, self.head, out_dtype=torch.float32, scale=self.logit_scale)
+        logits = ops.linear(h, self.head, out_dtype=torch.float32, scale=self.logit_scale)
+        if self.logit_softcap > 0.0:
+            logits = ops.softcap(logits, self.logit_softcap)          # cap * tanh(logits / cap), float32
+        return logits

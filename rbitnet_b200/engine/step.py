@@ -62,6 +62,10 @@ class StepContext:
     def state_view(self, entry: int):
         return self.cache.state(entry)
 
+    def part_state(self, entry: int, name: str):
+        """The state of a block's part other than its mixer (an input filter, say) for this run of the layer."""
+        return self.cache.state(("part", entry, name))
+
 
 def build_meta(chunks: List[SeqChunk], tokens: np.ndarray, want_rows: np.ndarray, device) -> StepMeta:
     T = int(tokens.shape[0])

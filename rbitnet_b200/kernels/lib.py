@@ -56,6 +56,17 @@ _SIGNATURES = {
     "rb_matrix_memory": [P, P, L, I, I, I, I, I, I, P, P, F, F, F, P, P, P, P, P, P, I, I, I, I, P],
     "rb_matrix_memory_lanes": [I],
     "rb_head_norm_gate": [P, I, P, P, P, L, I, I, I, I, I, F, I, I, P],
+    "rb_rmsnorm_grouped": [P, I, P, P, I, I, I, F, P],
+    "rb_input_filter": [P, P, I, P, P, P, P, P, I, I, I, P],
+    "rb_gated_add": [P, P, P, L, I, P, I, I, P],
+    "rb_add_scaled_rows": [P, P, P, L, I, I, P],
+    "rb_softcap": [P, ctypes.c_longlong, F, P],
+    "rb_gla_decay": [P, P, L, I, P, P, I, I, I, F, P],
+    "rb_gla_max_dim": [],
+    "rb_gla_scan": [P, P, L, I, I, I, P, F, P, P, P, P, I, I, I, I, P],
+    "rb_latent_norm_append": [P, I, P, L, I, I, I, I, P, P, F, P, P, I, I, I, P, P, I, P],
+    "rb_route_scored": [P, P, P, L, I, P, P, I, I, I, I, I, I, P, I, I, P, P],
+    "rb_routed_gather_scaled": [P, P, L, I, P, P, P, I, I, I, P],
     "rb_attention_simple": [P, P, I, P, P, P, I, I, P, P, I, I, I, I, F, I, P],
     "rb_sample": [P, P, L, I, I, P, P, P, P],
     "rb_sample_chunks": [I],
@@ -76,7 +87,7 @@ _SIGNATURES = {
 
 
 #: source files whose kernels address the cache through the checked function (each has its own word)
-CHECKED_FILES = ("elementwise", "gemm_tcgen05", "attention_simple", "attention_tiled")
+CHECKED_FILES = ("elementwise", "gemm_tcgen05", "attention_simple", "attention_tiled", "latent")
 
 
 class KernelError(RuntimeError):

@@ -48,6 +48,30 @@ class GateUpWeight:
 
 
 @dataclass
+class PerHeadWeight:
+    """One matrix [n_out, n_in] per head, made ready for ``per_head_linear``: ``w`` is [heads, n_out, n_in]."""
+    w: torch.Tensor
+    heads: int
+    n_out: int
+    n_in: int
+
+
+@dataclass
+class ExpertGateUp:
+    """The gate and up matrices of gated experts, one expert below the other (``rows`` rows each).
+    ``block == 0``: an expert's rows are [gate | up].  ``block == 16``: the interleaved layout of ``GateUpWeight``."""
+    w: torch.Tensor
+    inner: int
+    n_in: int
+    rows: int
+    block: int = 0
+
+    @property
+    def n_out(self):
+        return self.w.shape[0]
+
+
+@dataclass
 class NormRequest:
     """Asks the product that adds to the residual stream to leave what the norm after it needs
     (``CudaOps.linear(..., then_norm=request)``).  ``result`` is the ``NormedRows`` if it did."""
@@ -725,6 +749,134 @@ class CudaOps:
                       at["g"], T, H, Dv, float(p.norm_eps), 1, 1, self._stream())
         return out
 
+
+    # ------------------------------------------------------------------ around a sublayer
+    def rmsnorm_grouped(self, x: torch.Tensor, w: torch.Tensor, groups: int, eps: float, out_dtype=None) -> torch.Tensor:
+        """The row cut into ``groups`` equal consecutive parts, each divided by its own root mean square (eps under the
+        root), the whole times w; float32 arithmetic, the result in the compute dtype."""
+        self._check(x, torch.float32, "rmsnorm_grouped input")
+        T, E = x.shape
+        out = torch.empty((T, E), dtype=out_dtype or self.dtype, device=self.device)
+        self.lib.call("rb_rmsnorm_grouped", _ptr(out), _CODE[out.dtype], _ptr(x), _ptr(w), T, E, int(groups), float(eps),
+                      self._stream())
+        return out
+
+    def input_filter(self, h: torch.Tensor, taps: torch.Tensor, ring: Optional[torch.Tensor], meta) -> torch.Tensor:
+        """h_t + sum_j taps[:, j] h_(t - K + 1 + j) over a sequence's rows (float32 sums, the result in h's dtype).  The
+        sequence's last inputs live in ``ring`` (float32 [n_slots, K, width], a row per position modulo K), which moves on."""
+        self._check(h, self.dtype, "input_filter rows")
+        T, C = h.shape
+        K = taps.shape[1]
+        first, count, tok_first, n_runs = self._runs(meta)
+        out = torch.empty_like(h)
+        self.lib.call("rb_input_filter", _ptr(out), _ptr(h), self.code, _ptr(taps), _ptr(ring), _ptr(tok_first),
+                      _ptr(meta.tok_slot), _ptr(meta.tok_pos), T, C, K, self._stream())
+        if first is not None and K > 1:
+            self.lib.call("rb_conv_tail_update", _ptr(ring), _ptr(h), h.stride(0), 0, self.code, c_void_p(0), _ptr(first),
+                          _ptr(count), _ptr(meta.tok_slot), _ptr(meta.tok_pos), n_runs, C, K, self._stream())
+        return out
+
+    def gated_add(self, x: torch.Tensor, y: torch.Tensor, logits: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+        """x += y * sigmoid(logits + bias), value by value, in float32."""
+        self._check(x, torch.float32, "gated_add target")
+        self._check(y, torch.float32, "gated_add result")
+        T, E = x.shape
+        self.lib.call("rb_gated_add", _ptr(x), _ptr(y), _ptr(logits), logits.stride(0), _CODE[logits.dtype], _ptr(bias), T, E,
+                      self._stream())
+        return x
+
+    def add_scaled_rows(self, y: torch.Tensor, z: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+        """y += sigmoid(gate[t]) * z, one number per row; float32."""
+        self._check(y, torch.float32, "add_scaled_rows target")
+        self._check(z, torch.float32, "add_scaled_rows rows")
+        T, E = y.shape
+        self.lib.call("rb_add_scaled_rows", _ptr(y), _ptr(z), _ptr(gate), gate.stride(0), T, E, self._stream())
+        return y
+
+    def softcap(self, v: torch.Tensor, cap: float) -> torch.Tensor:
+        """v <- cap * tanh(v / cap), in place (float32)."""
+        self._check(v, torch.float32, "softcap values")
+        self.lib.call("rb_softcap", _ptr(v), v.numel(), float(cap), self._stream())
+        return v
+
+    # ------------------------------------------------------------------ gated linear attention
+    def gated_linear_attention(self, proj: torch.Tensor, p, state, meta) -> torch.Tensor:
+        """The recurrence of ``parts.gla.GatedLinearAttention`` ``p`` on float32 rows [q | k | v | g | A1 h] of its stacked
+        projection: the decays, the memory's steps, the heads' outputs under their norm, weight and SiLU gate as
+        [T, H * value_dim] in the compute dtype.  The sequences' memory (``state["S"]``, by value column) moves on."""
+        self._check(proj, torch.float32, "gated_linear_attention projections")
+        T, H, D, Dv, R = proj.shape[0], p.n_heads, p.head_dim, p.value_dim, p.decay_rank
+        if D > self.lib.raw("rb_gla_max_dim")():
+            raise KernelError(f"gated linear attention: {D} key channels per head are more than the kernel holds")
+        at = p.offsets()
+        first, count, _, n_runs = self._runs(meta)
+        alpha = torch.empty((T, H * D), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_gla_decay", _ptr(alpha), _ptr(proj), proj.stride(0), at["a"], _ptr(p.a2), _ptr(p.a2_bias), T, H * D, R,
+                      float(p.tau), self._stream())
+        o = torch.empty((T, H * Dv), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_gla_scan", _ptr(o), _ptr(proj), proj.stride(0), at["q"], at["k"], at["v"], _ptr(alpha),
+                      float(D) ** -0.5, _ptr(state["S"]), _ptr(first), _ptr(count), _ptr(meta.tok_slot), n_runs, H, D, Dv,
+                      self._stream())
+        out = torch.empty((T, H * Dv), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_head_norm_gate", _ptr(out), self.code, _ptr(o), _ptr(p.norm_w), _ptr(proj), proj.stride(0), F32,
+                      at["g"], T, H, Dv, float(p.norm_eps), 1, 1, self._stream())
+        return out
+
+    # ------------------------------------------------------------------ attention through latents
+    def latent_norm_append(self, down: torch.Tensor, q_rank: int, kv_rank: int, wq: torch.Tensor, wkv: torch.Tensor,
+                           eps: float, meta, view) -> torch.Tensor:
+        """From float32 rows [query latent | key/value latent]: each under its RMS norm and weight; the query latent is
+        returned ([T, q_rank], compute dtype), the other goes to the sequence's page (``view.head_dim`` wide, padded
+        with zeros)."""
+        self._check(down, torch.float32, "latent_norm_append rows")
+        T = down.shape[0]
+        cq = torch.empty((T, q_rank), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_latent_norm_append", _ptr(cq), self.code, _ptr(down), down.stride(0), 0, q_rank, q_rank, kv_rank,
+                      _ptr(wq), _ptr(wkv), float(eps), _ptr(view.k), _ptr(view.page_table), view.max_pages, view.page_size,
+                      view.head_dim, _ptr(meta.tok_pos), _ptr(meta.tok_slot), T, self._stream())
+        return cq
+
+    def prepare_per_head(self, w: torch.Tensor) -> PerHeadWeight:
+        """[heads, n_out, n_in] -> ready for ``per_head_linear``."""
+        w = self.to_compute(w)
+        return PerHeadWeight(w, w.shape[0], w.shape[1], w.shape[2])
+
+    def per_head_linear(self, x: torch.Tensor, weight: PerHeadWeight) -> torch.Tensor:
+        """x [T, heads * n_in] -> [T, heads * n_out]: head h's values times its own matrix (float32 sums)."""
+        self._check(x, self.dtype, "per_head_linear input")
+        T, H, N, K = x.shape[0], weight.heads, weight.n_out, weight.n_in
+        if x.shape[1] != H * K:
+            raise KernelError(f"per_head_linear: rows of {x.shape[1]} values are not {H} heads of {K}")
+        out = torch.empty((T, H * N), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_gemm_simple_batched", _ptr(out), out.stride(0), self.code, _ptr(x), x.stride(0), _ptr(weight.w), K,
+                      self.code, T, N, K, 0, 1.0, H, N, K, N * K, self._stream())
+        return out
+
+    # ------------------------------------------------------------------ routed experts, the variants
+    def prepare_expert_gate_up(self, gates: List[torch.Tensor], ups: List[torch.Tensor]) -> ExpertGateUp:
+        """The gated experts' first matrices, one expert below the other, an expert's rows [gate | up]."""
+        inner, K = gates[0].shape
+        w = torch.cat([torch.cat([self.to_compute(g), self.to_compute(u)], dim=0) for g, u in zip(gates, ups)], dim=0)
+        return ExpertGateUp(w.contiguous(), inner, K, 2 * inner, 0)
+
+    def route_scored(self, h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int,
+                     keep: int, scoring: str = "softmax", extra_rows: int = 0, router_tc: Optional[LinearWeight] = None):
+        """``route`` with its variants: ``scoring`` "sigmoid" takes s = sigmoid(z) output by output; the last
+        ``extra_rows`` rows of ``router`` are no outputs: their float32 sums are returned as they are ([T, extra_rows],
+        None without).  Returns (ids, weights, extra)."""
+        self._check(h, self.dtype, "route input")
+        T, K = h.shape
+        n = router.shape[0] - extra_rows
+        ids = torch.empty((T, top), dtype=torch.int32, device=self.device)
+        weights = torch.empty((T, top), dtype=torch.float32, device=self.device)
+        extra = torch.empty((T, extra_rows), dtype=torch.float32, device=self.device) if extra_rows else None
+        z = torch.empty((T, n + extra_rows), dtype=torch.float32, device=self.device) if T >= 64 else None
+        self.lib.call("rb_route_scored", _ptr(ids), _ptr(weights), _ptr(h), h.stride(0), self.code, _ptr(router),
+                      _ptr(correction), T, K, n, int(top), int(groups), int(keep), _ptr(z),
+                      {"softmax": 0, "sigmoid": 1}[scoring], int(extra_rows), _ptr(extra), self._stream(),
+                      launches=2 if z is not None else 1)
+        return ids, weights, extra
+
     # ------------------------------------------------------------------ routed experts
     def prepare_router(self, router: torch.Tensor) -> Optional[LinearWeight]:
         """The router's matrix for the tensor-core product, if that product gives the float32 sums: in bfloat16 mode, for
@@ -769,11 +921,15 @@ class CudaOps:
     def _routed_on_tensor_cores(self, inner: int, width: int) -> bool:
         return self.dtype == torch.bfloat16 and inner % 8 == 0 and width % 8 == 0
 
-    def routed_experts(self, h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_up: LinearWeight,
-                       w_down: LinearWeight, n_experts: int, inner: int, accumulate_into: Optional[torch.Tensor] = None):
+    def routed_experts(self, h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_up, w_down: LinearWeight,
+                       n_experts: int, inner: int, accumulate_into: Optional[torch.Tensor] = None, act=None,
+                       weight_on_input: bool = False):
         """sum_j weights[t, j] * expert(ids[t, j])(h[t]) with expert e: W_down_e relu2(W_up_e h); ids >= n_experts are
         identity experts (h[t] itself).  ``w_up``: [n_experts * inner, width], ``w_down``: [n_experts * width, inner].
-        Added to ``accumulate_into`` (float32), or returned as float32 rows."""
+        Added to ``accumulate_into`` (float32), or returned as float32 rows.
+        ``act`` = (alpha, limit, shift): gated experts, ``w_up`` an ``ExpertGateUp``, the inner rows
+        g' sigmoid(alpha g') (u' + shift) as in ``gated_linear``.  ``weight_on_input``: sum_j expert(weights[t, j] * h[t])
+        instead (the weighted row is rounded to the compute dtype before the expert's first product)."""
         T, E = h.shape
         top = ids.shape[1]
         pairs = T * top
@@ -791,10 +947,35 @@ class CudaOps:
             self.lib.call("rb_routed_plan", _ptr(pos), _ptr(row_token), _ptr(tile_group), _ptr(ids), pairs, top, n_experts,
                           tile, n_tiles, self._stream())
             xp = torch.empty((rows, E), dtype=self.dtype, device=self.device)
-            self.lib.call("rb_routed_gather", _ptr(xp), _ptr(h), h.stride(0), self.code, _ptr(row_token), rows, E, self._stream())
+            if weight_on_input:
+                self.lib.call("rb_routed_gather_scaled", _ptr(xp), _ptr(h), h.stride(0), self.code, _ptr(row_token), _ptr(pos),
+                              _ptr(weights), top, rows, E, self._stream())
+            else:
+                self.lib.call("rb_routed_gather", _ptr(xp), _ptr(h), h.stride(0), self.code, _ptr(row_token), rows, E, self._stream())
             mid = torch.empty((rows, inner), dtype=self.dtype, device=self.device)
             y = torch.empty((rows, E), dtype=torch.float32, device=self.device)
-            if self._routed_on_tensor_cores(inner, E):
+            if act is not None:
+                # gated experts: the grouped product leaves float32 [gate | up] rows, a kernel makes the inner rows
+                per = w_up.rows
+                gu = torch.empty((rows, per), dtype=torch.float32, device=self.device)
+                tc = self._routed_on_tensor_cores(inner, E)
+                if tc:
+                    self.lib.call("rb_gemm_tc_grouped", _ptr(tile_group), launches=0)
+                    self.lib.call("rb_gemm_tc", _ptr(gu), gu.stride(0), F32, _ptr(xp), xp.stride(0), rows, _ptr(w_up.w),
+                                  w_up.w.stride(0), n_experts * per, per, E, 0, 0, 1, tile, 1.0, self._stream())
+                else:
+                    self.lib.call("rb_gemm_grouped_simple", _ptr(gu), gu.stride(0), F32, _ptr(xp), xp.stride(0), _ptr(w_up.w),
+                                  w_up.w.stride(0), self.code, _ptr(tile_group), rows, per, E, 0, self._stream())
+                self.lib.call("rb_gated_act", _ptr(mid), _ptr(gu), self.code, F32, rows, inner, gu.stride(0), w_up.block,
+                              float(act[0]), float(act[1]), float(act[2]), self._stream())
+                if tc:
+                    self.lib.call("rb_gemm_tc_grouped", _ptr(tile_group), launches=0)
+                    self.lib.call("rb_gemm_tc", _ptr(y), y.stride(0), F32, _ptr(mid), mid.stride(0), rows, _ptr(w_down.w),
+                                  w_down.w.stride(0), n_experts * E, E, inner, 0, 0, 1, tile, 1.0, self._stream())
+                else:
+                    self.lib.call("rb_gemm_grouped_simple", _ptr(y), y.stride(0), F32, _ptr(mid), mid.stride(0), _ptr(w_down.w),
+                                  w_down.w.stride(0), self.code, _ptr(tile_group), rows, E, inner, 0, self._stream())
+            elif self._routed_on_tensor_cores(inner, E):
                 self.lib.call("rb_gemm_tc_square_relu", launches=0)
                 self.lib.call("rb_gemm_tc_grouped", _ptr(tile_group), launches=0)
                 self.lib.call("rb_gemm_tc", _ptr(mid), mid.stride(0), self.code, _ptr(xp), xp.stride(0), rows, _ptr(w_up.w),
@@ -810,7 +991,7 @@ class CudaOps:
         else:
             pos = torch.full((pairs,), -1, dtype=torch.int32, device=self.device)
         self.lib.call("rb_routed_combine", _ptr(out), out.stride(0), _ptr(y), _ptr(h), h.stride(0), self.code, _ptr(pos),
-                      _ptr(weights), T, top, E, acc, self._stream())
+                      _ptr(None if weight_on_input else weights), T, top, E, acc, self._stream())
         return out
 
     def gather_rows(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

@@ -1,13 +1,17 @@
 from .spec import PartSpec, BlockSpec, ScheduleEntry, ModelSpec
-from .base import Part, Norm, PositionEncoding, Mixer, FeedForward, Connection, CacheNeed, StateNeed
+from .base import (Part, Norm, PositionEncoding, Mixer, FeedForward, Connection, CacheNeed, StateNeed, InputFilter,
+                   ResultGate)
 from .registry import register_part, unregister_part, known_parts, build_part, build_block
 from .norm import RMSNorm, LayerNorm
 from .position import RotaryEncoding, NoPositionEncoding
 from .attention import Attention
 from .feed_forward import GatedDense, Dense, RoutedExperts
-from .block import PreNormBlock, StreamBlock
+from .block import PreNormBlock, StreamBlock, GatedPreNormBlock
 from .recurrent import GatedLinearRecurrence, MatrixMemory
 from .delta import GatedDeltaRule
+from .gla import GatedLinearAttention
+from .latent import LatentAttention
+from .sublayer import CausalTapsFilter, SigmoidGate
 from .parallel import ParallelMixers
 from .connection import ResidualConnection, HyperConnection
 
@@ -16,4 +20,5 @@ __all__ = ["PartSpec", "BlockSpec", "ScheduleEntry", "ModelSpec", "Part", "Norm"
            "known_parts", "build_part", "build_block", "RMSNorm", "RotaryEncoding", "NoPositionEncoding", "Attention",
            "GatedDense", "PreNormBlock", "StreamBlock", "Connection", "GatedLinearRecurrence", "MatrixMemory",
            "ParallelMixers", "ResidualConnection", "HyperConnection", "LayerNorm", "Dense", "RoutedExperts",
-           "GatedDeltaRule"]
+           "GatedDeltaRule", "GatedLinearAttention", "LatentAttention", "CausalTapsFilter", "SigmoidGate",
+           "InputFilter", "ResultGate", "GatedPreNormBlock"]

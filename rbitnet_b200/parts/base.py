@@ -15,6 +15,10 @@ Roles:
                     several by name)
   feed_forward      forward(ctx, h, accumulate_into), likewise
   connection        how a sublayer's result enters the residual state (``weights()``)
+  input_filter      forward(ctx, h, state) -> what the sublayer reads instead of h (same shape and dtype); may keep
+                    fixed-size state per sequence (``state_need``), which the block hands to it
+  result_gate       logits(ctx, h) from the sublayer's unfiltered input, and apply(ctx, x, y, logits): how the
+                    sublayer's result y enters the residual stream x
 """
 from __future__ import annotations
 
@@ -101,6 +105,31 @@ class FeedForward(Part):
     role = "feed_forward"
 
     def forward(self, ctx, h: torch.Tensor, accumulate_into: Optional[torch.Tensor] = None):
+        raise NotImplementedError
+
+
+class InputFilter(Part):
+    """Replaces what a sublayer reads, h [T, E] in the compute dtype, by a function of h and of the sequence's
+    earlier rows.  ``state_need`` as for a mixer; the block keeps the state per run of the layer and hands the
+    run's tensor ([n_slots, *shape]) to ``forward``."""
+    role = "input_filter"
+
+    def state_need(self):
+        return None
+
+    def forward(self, ctx, h: torch.Tensor, state):
+        raise NotImplementedError
+
+
+class ResultGate(Part):
+    """Decides how much of a sublayer's result enters the residual stream, from the sublayer's input rows."""
+    role = "result_gate"
+
+    def logits(self, ctx, h: torch.Tensor):
+        raise NotImplementedError
+
+    def apply(self, ctx, x: torch.Tensor, y: torch.Tensor, logits) -> None:
+        """x (float32 [T, E], the residual stream) takes y (float32 [T, E]) in."""
         raise NotImplementedError
 
 

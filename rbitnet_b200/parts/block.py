@@ -148,5 +148,47 @@ class StreamBlock:
         return h
 
 
+class GatedPreNormBlock:
+    """Pre-norm sublayers whose inputs may be filtered and whose results may be gated:
+
+        h = norm(x);   x <- x + gate(h) * sublayer(filter(h))
+
+    for the mixer and, if the layer has one, the feed-forward.  Parts: "mixer", "mixer_norm" and optionally
+    "mixer_filter" (role "input_filter"), "mixer_gate" (role "result_gate"); "feed_forward" with "ffn_norm" and
+    optionally "ffn_filter", "ffn_gate".  Without a gate the sublayer adds its result itself; without a filter it
+    reads the normed rows.  A filter's per-sequence state belongs to the run of the layer
+    (``ctx.part_state(entry, name)``)."""
+
+    def __init__(self, spec):
+        self.spec = spec
+        self._parts = build_parts(spec)
+        missing = [n for n in ("mixer", "mixer_norm") if n not in self._parts]
+        if missing:
+            raise ValueError(f"a pre_norm_gated block needs the parts {missing}")
+        if ("feed_forward" in self._parts) != ("ffn_norm" in self._parts):
+            raise ValueError("a pre_norm_gated block has a feed-forward with its norm, or neither")
+        p = self._parts
+        self.sublayers = [(p["mixer"], p["mixer_norm"], "mixer_filter", p.get("mixer_filter"), p.get("mixer_gate"), True)]
+        if "feed_forward" in p:
+            self.sublayers.append((p["feed_forward"], p["ffn_norm"], "ffn_filter", p.get("ffn_filter"), p.get("ffn_gate"), False))
+        elif "ffn_filter" in p or "ffn_gate" in p:
+            raise ValueError("a pre_norm_gated block without a feed-forward has no filter or gate for one")
+
+    def parts(self):
+        return self._parts
+
+    def run(self, ctx, x, entry: int):
+        for part, norm, filter_name, filt, gate, is_mixer in self.sublayers:
+            h = norm.forward(ctx, x)
+            logits = gate.logits(ctx, h) if gate is not None else None
+            if filt is not None:
+                h = filt.forward(ctx, h, ctx.part_state(entry, filter_name))
+            into = x if gate is None else None
+            y = part.forward(ctx, h, entry, accumulate_into=into) if is_mixer else part.forward(ctx, h, accumulate_into=into)
+            if gate is not None:
+                gate.apply(ctx, x, y, logits)
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "pre_norm_gated", GatedPreNormBlock)
 register_part("block", "multi_stream", StreamBlock)

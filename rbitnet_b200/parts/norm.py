@@ -1,5 +1,7 @@
 """Norms over the model width.  RMSNorm: y = x * w / sqrt(mean(x^2) + eps), all in float32
 (crates/bitnet-core/src/llama/model.rs:93-100).  The weight multiplies directly (no 1+w).
+``groups`` > 1: the row is cut into that many equal consecutive parts, each divided by its own root mean
+square; the weight still spans the whole row.
 LayerNorm: the mean taken off first, and a bias added."""
 from __future__ import annotations
 
@@ -10,8 +12,10 @@ from .registry import register_part
 
 
 class RMSNorm(Norm):
-    def __init__(self, width: int, eps: float):
-        self.width, self.eps = int(width), float(eps)
+    def __init__(self, width: int, eps: float, groups: int = 1):
+        self.width, self.eps, self.groups = int(width), float(eps), int(groups)
+        if self.groups < 1 or self.width % self.groups:
+            raise ValueError(f"rmsnorm: a row of {self.width} values is not {self.groups} equal parts")
         self.weight = None
 
     def weight_shapes(self):
@@ -21,14 +25,17 @@ class RMSNorm(Norm):
         # exact in float32 whatever the stored dtype
         self.weight = weights["weight"].to(torch.float32).contiguous()
 
-    def forward(self, ctx, x):
-        return ctx.ops.rmsnorm(x, self.weight, self.eps)
+    def forward(self, ctx, x, out_dtype=None):
+        kw = {} if out_dtype is None else {"out_dtype": out_dtype}
+        if self.groups > 1:
+            return ctx.ops.rmsnorm_grouped(x, self.weight, self.groups, self.eps, **kw)
+        return ctx.ops.rmsnorm(x, self.weight, self.eps, **kw)
 
     def deferred(self, ops):
         """What a product before this norm needs to prepare it, if the operations can fold a norm
         into the products around it (see ``PreNormBlock``); else None."""
         make = getattr(ops, "norm_request", None)
-        return make(self.weight, self.eps) if make is not None else None
+        return make(self.weight, self.eps) if make is not None and self.groups == 1 else None
 
 
 class LayerNorm(Norm):

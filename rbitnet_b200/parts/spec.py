@@ -102,6 +102,11 @@ class ModelSpec:
     #: rows of residual state per token (1: the ordinary residual stream).  With more, the embedded row
     #: is copied into each at the start and the rows are added up before the final norm.
     residual_streams: int = 1
+    #: a norm on the embedded rows before the first layer (its result stays float32), with its tensor names by key
+    embedding_norm: Optional[PartSpec] = None
+    embedding_norm_names: Dict[str, str] = field(default_factory=dict)
+    #: the logits are capped softly: cap * tanh(logits / cap) (0.0: as they are)
+    logit_softcap: float = 0.0
 
     def tensor_table(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         """name -> (shape, init kind) of every tensor the model needs."""
@@ -118,6 +123,9 @@ class ModelSpec:
         norm = build_part("norm", self.final_norm)
         for key, (shape, kind) in norm.weight_shapes().items():
             table[self.final_norm_names[key]] = (tuple(shape), kind)
+        if self.embedding_norm is not None:
+            for key, (shape, kind) in build_part("norm", self.embedding_norm).weight_shapes().items():
+                table[self.embedding_norm_names[key]] = (tuple(shape), kind)
         if self.head_name is not None:
             table[self.head_name] = ((self.vocab_size, self.width), "matrix")
         return table

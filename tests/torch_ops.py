@@ -258,7 +258,102 @@ class TorchOps:
         gate = x[:, at["g"]:at["g"] + H * Dv]
         return (o.reshape(T, H * Dv) * (gate / (1.0 + torch.exp(-gate)))).to(self.dtype)
 
+    # ---- around a sublayer
+    def rmsnorm_grouped(self, x, w, groups, eps, out_dtype=None):
+        T, E = x.shape
+        parts = x.view(T, groups, E // groups)
+        y = parts / torch.sqrt((parts * parts).mean(-1, keepdim=True) + eps)
+        return (y.reshape(T, E) * w).to(out_dtype or self.dtype)
+
+    def input_filter(self, h, taps, ring, meta):
+        K = taps.shape[1]
+        x = h.to(torch.float32)
+        out = torch.zeros_like(x)
+        for first, n, slot in self._runs(meta):
+            old = ring[slot][1:] if K > 1 else torch.zeros(0, x.shape[1])     # this stand-in keeps the last K-1 inputs in rows 1..
+            hist = torch.cat([old, x[first:first + n]], dim=0)
+            for t in range(n):
+                out[first + t] = x[first + t] + (hist[t:t + K] * taps.T).sum(0)
+            if K > 1:
+                ring[slot][1:] = hist[n:n + K - 1]
+        return out.to(self.dtype)
+
+    def gated_add(self, x, y, logits, bias):
+        z = logits.to(torch.float32) + (bias if bias is not None else 0.0)
+        x += y * torch.sigmoid(z)
+        return x
+
+    def add_scaled_rows(self, y, z, gate):
+        y += torch.sigmoid(gate[:, :1]) * z
+        return y
+
+    def softcap(self, v, cap):
+        v.copy_(cap * torch.tanh(v / cap))
+        return v
+
+    # ---- gated linear attention
+    def gated_linear_attention(self, proj, p, state, meta):
+        H, D, Dv, R = p.n_heads, p.head_dim, p.value_dim, p.decay_rank
+        at = p.offsets()
+        x = proj.float()
+        T = x.shape[0]
+        z = x[:, at["a"]:at["a"] + R] @ p.a2.T + p.a2_bias
+        alpha = torch.exp(torch.nn.functional.logsigmoid(z) / p.tau).view(T, H, D)
+        q = x[:, at["q"]:at["q"] + H * D].view(T, H, D) * D ** -0.5
+        k = x[:, at["k"]:at["k"] + H * D].view(T, H, D)
+        v = x[:, at["v"]:at["v"] + H * Dv].view(T, H, Dv)
+        o = torch.zeros(T, H, Dv)
+        for first, n, slot in self._runs(meta):
+            S = state["S"][slot].clone()                                        # [H, Dv, D]
+            for t in range(first, first + n):
+                S = S * alpha[t][:, None, :] + v[t][:, :, None] * k[t][:, None, :]
+                o[t] = torch.einsum("hvd,hd->hv", S, q[t])
+            state["S"][slot] = S
+        o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + p.norm_eps) * p.norm_w
+        gate = x[:, at["g"]:at["g"] + H * Dv]
+        return (o.reshape(T, H * Dv) * (gate / (1.0 + torch.exp(-gate)))).to(self.dtype)
+
+    # ---- attention through latents
+    def latent_norm_append(self, down, q_rank, kv_rank, wq, wkv, eps, meta, view):
+        x = down.float()
+        cq, c = x[:, :q_rank], x[:, q_rank:q_rank + kv_rank]
+        cq = cq / torch.sqrt((cq * cq).mean(-1, keepdim=True) + eps) * wq
+        c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * wkv
+        for t in range(x.shape[0]):
+            p, slot = int(meta.tok_pos[t]), int(meta.tok_slot[t])
+            page = int(view.page_table[slot, p // view.page_size])
+            view.k[page, 0, p % view.page_size, :] = 0
+            view.k[page, 0, p % view.page_size, :kv_rank] = c[t].to(view.k.dtype)
+        return cq.to(self.dtype)
+
+    def prepare_per_head(self, w):
+        return self.to_compute(w)
+
+    def per_head_linear(self, x, w):
+        H, N, K = w.shape
+        y = torch.einsum("thk,hnk->thn", x.to(torch.float32).view(x.shape[0], H, K), w.to(torch.float32))
+        return y.reshape(x.shape[0], H * N).to(self.dtype)
+
     # ---- routed experts
+    def prepare_expert_gate_up(self, gates, ups):
+        w = torch.cat([torch.cat([self.to_compute(g), self.to_compute(u)], dim=0) for g, u in zip(gates, ups)], dim=0)
+        return _W(w, w.shape[0], w.shape[1])
+
+    def route_scored(self, h, router, correction, top, groups, keep, scoring="softmax", extra_rows=0, router_tc=None):
+        z = h.to(torch.float32) @ router.T
+        n = router.shape[0] - extra_rows
+        extra = z[:, n:].clone() if extra_rows else None
+        z = z[:, :n]
+        s = torch.sigmoid(z) if scoring == "sigmoid" else torch.softmax(z, dim=-1)
+        choice = s + correction if correction is not None else s.clone()
+        if groups > 1 and keep < groups:
+            per = n // groups
+            best = choice.view(-1, groups, per).max(-1).values
+            kept = torch.zeros_like(best, dtype=torch.bool).scatter_(1, best.topk(keep, dim=-1).indices, True)
+            choice = choice.masked_fill(~kept.repeat_interleave(per, dim=1), -math.inf)
+        ids = choice.topk(top, dim=-1).indices
+        return ids.to(torch.int32), s.gather(1, ids), extra
+
     def route(self, h, router, correction, top, groups, keep):
         s = torch.softmax(h.to(torch.float32) @ router.T, dim=-1)
         choice = s + correction if correction is not None else s.clone()
@@ -270,7 +365,8 @@ class TorchOps:
         ids = choice.topk(top, dim=-1).indices
         return ids.to(torch.int32), s.gather(1, ids)
 
-    def routed_experts(self, h, ids, weights, w_up, w_down, n_experts, inner, accumulate_into=None):
+    def routed_experts(self, h, ids, weights, w_up, w_down, n_experts, inner, accumulate_into=None, act=None,
+                       weight_on_input=False):
         T, E = h.shape
         x = h.to(torch.float32)
         out = torch.zeros(T, E)
@@ -279,10 +375,17 @@ class TorchOps:
                 if e >= n_experts:
                     out[t] += w * x[t]
                     continue
-                up = w_up.w[e * inner:(e + 1) * inner].to(torch.float32)
                 down = w_down.w[e * E:(e + 1) * E].to(torch.float32)
-                mid = (torch.clamp(up @ x[t], min=0.0) ** 2).to(self.dtype).to(torch.float32)
-                out[t] += w * (down @ mid)
+                xin = (w * x[t]).to(self.dtype).to(torch.float32) if weight_on_input else x[t]
+                if act is not None:
+                    gu = w_up.w[e * 2 * inner:(e + 1) * 2 * inner].to(torch.float32) @ xin
+                    alpha, limit, shift = act
+                    g, u = torch.clamp(gu[:inner], max=limit), torch.clamp(gu[inner:], -limit, limit)
+                    mid = (g / (1.0 + torch.exp(-alpha * g)) * (u + shift)).to(self.dtype).to(torch.float32)
+                else:
+                    up = w_up.w[e * inner:(e + 1) * inner].to(torch.float32)
+                    mid = (torch.clamp(up @ xin, min=0.0) ** 2).to(self.dtype).to(torch.float32)
+                out[t] += (down @ mid) if weight_on_input else w * (down @ mid)
         if accumulate_into is not None:
             accumulate_into += out
             return accumulate_into
