@@ -529,20 +529,44 @@ def _vaderax_shape(width, heads, kv, dim, delta_heads, delta_kv, delta_dim, delt
     return cfg
 
 
+def _nifarax_shape(width, mem_heads, mem_dim, mem_vdim, heads, dim, q_rank, kv_rank, experts, top, expert_ff, shared_ff, runs,
+                   vocab=32000):
+    """Layer sizes in the manner of a real model: of every three runs of a layer the first is gated linear attention and
+    two are attention through latents; every layer routes `top` of `experts` gated experts beside a shared one; the
+    fourth run (a memory layer again) uses the first layer's tensors."""
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "router": {"experts": experts, "top": top},
+           "shared": {"ff": shared_ff, "limit": 7.0}}
+    mem = {"type": "gla", "mixer": {"heads": mem_heads, "dim": mem_dim, "vdim": mem_vdim, "tau": 16.0, "decay_rank": 16}, "mlp": moe}
+    att = {"type": "latent_attention", "mlp": moe,
+           "mixer": {"heads": heads, "dim": dim, "vdim": dim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": dim ** -0.5}}
+    ls = [dict(mem) if i % 3 == 0 else dict(att) for i in range(runs)]
+    if runs >= 4:
+        ls[3]["weights_of"] = 0
+    return {"architecture": "Nifarax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 2}, "canon": {"taps": 4},
+            "logit_softcap": 30.0, "max_positions": 8192, "layers": ls}
+
+
 DESIGN_SIZES = {
-    # name: (the design's configuration, Llama configuration of equal width, layers, feed-forward and attention heads)
+    # name: (the design's configuration, the configuration of equal width, layer runs and feed-forward size beside it)
     "w2048": (_safuvik_shape(2048, 16, 4, 128, 64, 1024, 16, 8, 128, 256, 5632, 6), _llama_like(2048, 16, 4, 128, 5632, 6)),
     "w4096": (_safuvik_shape(4096, 32, 8, 128, 128, 1024, 16, 8, 256, 512, 14336, 3), _llama_like(4096, 32, 8, 128, 14336, 3)),
     # Vaderax: 4 stored layers of which two run twice (6 runs) beside 6 Llama layers; 3 layers beside 3
     "vaderax_w2048": (_vaderax_shape(2048, 16, 4, 128, 16, 8, 128, 128, 5632, 30, 4, 1408, 4), _llama_like(2048, 16, 4, 128, 5632, 6)),
     "vaderax_w4096": (_vaderax_shape(4096, 32, 8, 128, 32, 16, 128, 128, 14336, 62, 8, 1792, 3), _llama_like(4096, 32, 8, 128, 14336, 3)),
+    # Nifarax beside Vaderax (a matrix memory per head, attention and routed experts both): 6 runs of a layer beside 6, 3 beside 3
+    "nifarax_w2048": (_nifarax_shape(2048, 8, 128, 256, 16, 128, 768, 128, 32, 4, 1408, 1408, 6),
+                      _vaderax_shape(2048, 16, 4, 128, 16, 8, 128, 128, 5632, 30, 4, 1408, 4)),
+    "nifarax_w4096": (_nifarax_shape(4096, 16, 128, 256, 32, 128, 1536, 256, 64, 8, 1792, 1792, 3),
+                      _vaderax_shape(4096, 32, 8, 128, 32, 16, 128, 128, 14336, 62, 8, 1792, 3)),
 }
 
 
 class DesignTimer(KernelTimer):
     """KernelTimer with the operations of the recurrent mixers and of the residual streams."""
     OPS = KernelTimer.OPS + ("stream_step", "normed_mean", "streams_expand", "streams_sum", "norm_rotate_append", "head_gate",
-                             "gated_recurrence", "matrix_memory", "layernorm", "add_rows", "gated_delta", "route", "routed_experts")
+                             "gated_recurrence", "matrix_memory", "layernorm", "add_rows", "gated_delta", "route", "routed_experts",
+                             "rmsnorm_grouped", "input_filter", "gated_add", "add_scaled_rows", "softcap", "gated_linear_attention",
+                             "latent_norm_append", "per_head_linear", "route_scored")
 
     @staticmethod
     def _describe(name, a, kw, sync=True):
@@ -578,7 +602,32 @@ class DesignTimer(KernelTimer):
             return (f"delta rule: convolution, unit vectors, gates, recurrence, head norm and gate [{T} rows, {p.n_heads} heads of "
                     f"{p.head_dim}x{p.value_dim}]", el(proj) + T * p.n_heads * p.value_dim * 2,
                     0.0)
-        if name == "route":
+        if name == "gated_linear_attention":
+            proj, p = a[0], a[1]
+            T = proj.shape[0]
+            return (f"gated linear attention: decays, recurrence, head norm and gate [{T} rows, {p.n_heads} heads of "
+                    f"{p.head_dim}x{p.value_dim}]",
+                    T * (2 * p.n_heads * p.head_dim + 2 * p.n_heads * p.value_dim + p.decay_rank) * 4 + T * p.n_heads * p.value_dim * 2, 0.0)
+        if name == "latent_norm_append":
+            down, qr, kr = a[0], a[1], a[2]
+            T = down.shape[0]
+            return f"latents' norms + append [{T} rows of {qr}+{kr}]", el(down) + T * (qr + kr) * 2, 0.0
+        if name == "per_head_linear":
+            x, w = a[0], a[1]
+            T = x.shape[0]
+            return (f"product per head [{T}x{w.heads}x{w.n_in}]x[{w.n_out}x{w.n_in}]", el(x) + el(w.w) + T * w.heads * w.n_out * 2,
+                    2.0 * T * w.heads * w.n_out * w.n_in)
+        if name == "input_filter":
+            return f"input filter [{a[0].shape[0]} rows, {a[1].shape[1]} taps]", 2 * el(a[0]), 0.0
+        if name == "gated_add":
+            return f"gated residual [{a[0].shape[0]} rows]", 3 * el(a[0]) + el(a[2]), 0.0
+        if name == "add_scaled_rows":
+            return f"shared expert's gate and sum [{a[0].shape[0]} rows]", 3 * el(a[0]), 0.0
+        if name == "softcap":
+            return f"soft cap [{a[0].shape[0]} rows]", 2 * el(a[0]), 0.0
+        if name == "rmsnorm_grouped":
+            return f"rmsnorm in groups [{a[0].shape[0]} rows]", el(a[0]) + a[0].numel() * 2, 0.0
+        if name in ("route", "route_scored"):
             h, router = a[0], a[1]
             return f"router [{h.shape[0]} rows, {router.shape[0]} outputs]", el(h) + el(router), 0.0
         if name == "routed_experts":
@@ -586,8 +635,11 @@ class DesignTimer(KernelTimer):
             T, E = h.shape
             pairs = T * ids.shape[1]
             used = min(1.0, pairs / max(a[5], 1))          # the share of the experts' matrices a step has to read at least
-            return (f"routed experts: plan, gather, two grouped products, weighted sum [{T} rows, {ids.shape[1]} of {a[5]} experts of {inner}]",
-                    int(used * (el(w_up.w) + el(w_down.w))) + pairs * (E * 2 + E * 4) + 2 * T * E * 4, 4.0 * pairs * E * inner)
+            gated = kw.get("act") is not None
+            return (f"routed experts: plan, gather, two grouped products{' with the gate between' if gated else ''}, sum "
+                    f"[{T} rows, {ids.shape[1]} of {a[5]} experts of {inner}]",
+                    int(used * (el(w_up.w) + el(w_down.w))) + pairs * (E * 2 + E * 4) + 2 * T * E * 4,
+                    (6.0 if gated else 4.0) * pairs * E * inner)
         if name in ("layernorm", "add_rows"):
             return f"{name} [{a[0].shape[0]} rows]", (2 if name == "layernorm" else 3) * el(a[0]), 0.0
         if name in ("normed_mean", "streams_expand", "streams_sum"):
@@ -606,7 +658,9 @@ def run_design(name, args):
     design = str(DESIGN_SIZES[name][0].get("architecture", "design"))
     out = {"design": f"{design} beside Llama", "size": name, "peaks": pk, "dtype": "bf16", "data": "synthetic (random weights)",
            "batch": args.batch, "context": args.context, "prefill_tokens": args.prefill_tokens, "models": {}}
-    for label, cfg in zip((design.lower(), "llama"), DESIGN_SIZES[name]):
+    beside = str(DESIGN_SIZES[name][1].get("architecture", "llama")).lower()
+    out["design"] = f"{design} beside {beside.capitalize()}"
+    for label, cfg in zip((design.lower(), beside), DESIGN_SIZES[name]):
         room = steps + warmup + 16
         ctx = args.context
         max_tokens = max(args.batch * (-(-(ctx + room) // 64) * 64), args.prefill_tokens + 64) + 64 * 8
@@ -616,7 +670,7 @@ def run_design(name, args):
                 pool.normal_(0.0, 1.0)
         torch.cuda.synchronize()
         if args.timeline:
-            if label != "llama":
+            if label != beside:
                 print_timeline(engine, args.batch, ctx)
             continue
         pf_ms = time_prefill(engine, args.prefill_tokens)
@@ -686,7 +740,8 @@ def main():
                     help="run one of the other generation workloads end to end instead (one short line)")
     ap.add_argument("--design", default=None, choices=sorted(DESIGN_SIZES),
                     help="instead of the headline: prefill and decode of another design (Safuvik; vaderax_*: Vaderax) beside the Llama decoder of "
-                         "equal size at these layer sizes (uses --batch, --context, --prefill-tokens, --steps)")
+                         "equal size at these layer sizes, nifarax_*: Nifarax beside Vaderax (uses --batch, --context, --prefill-tokens, "
+                         "--steps)")
     args = ap.parse_args()
 
     if args.impl == "reference":

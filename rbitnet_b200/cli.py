@@ -73,7 +73,9 @@ def cmd_inspect(args) -> int:
     cfg.sizes_from_tensors({name: tuple(t.shape) for name, t in tensors.items()})
     spec = get_architecture(cfg.architecture).build_spec(cfg)
     n = sum(t.numel() for t in tensors.values())
-    print(f"{cfg.architecture}: {len(spec.layers)} layers, width {spec.width}, vocabulary {spec.vocab_size}, "
+    runs = len(spec.schedule)
+    again = f" ({runs} runs of a layer in a pass)" if runs != len(spec.layers) else ""
+    print(f"{cfg.architecture}: {len(spec.layers)} layers{again}, width {spec.width}, vocabulary {spec.vocab_size}, "
           f"{len(tensors)} tensors, {n} parameters")
     for k, v in cfg.to_dict().items():
         print(f"  {k}: {v}")
