@@ -61,8 +61,11 @@ _SIGNATURES = {
     "rb_gated_add": [P, P, P, L, I, P, I, I, P],
     "rb_add_scaled_rows": [P, P, P, L, I, I, P],
     "rb_softcap": [P, ctypes.c_longlong, F, P],
-    "rb_gla_decay": [P, P, L, I, P, P, I, I, I, F, P],
+    "rb_gla_decay": [P, P, L, I, P, P, I, I, I, F, I, P],
     "rb_gla_max_dim": [],
+    "rb_gla_chunked_supports": [I, I, L, I, I, I],
+    "rb_gla_chunk_floats": [I],
+    "rb_gla_chunked": [P, P, L, I, I, I, P, F, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
     "rb_gla_scan": [P, P, L, I, I, I, P, F, P, P, P, P, I, I, I, I, P],
     "rb_latent_norm_append": [P, I, P, L, I, I, I, I, P, P, F, P, P, I, I, I, P, P, I, P],
     "rb_route_scored": [P, P, P, L, I, P, P, I, I, I, I, I, I, P, I, I, P, P],

@@ -150,6 +150,8 @@ class CudaOps:
         self.fuse_recurrent_step = True
         #: the delta rule takes runs of several tokens in chunks of 32 (else token by token, as a decode step does)
         self.delta_in_chunks = True
+        #: so does gated linear attention
+        self.gla_in_chunks = True
         #: a decode step's delta rule (convolution to gate) is one kernel while rows x heads fit the SMs
         self.fuse_delta_step = True
         #: tensor-core products of more than 256 tokens may share a weight tile's inner dimension
@@ -810,13 +812,25 @@ class CudaOps:
             raise KernelError(f"gated linear attention: {D} key channels per head are more than the kernel holds")
         at = p.offsets()
         first, count, _, n_runs = self._runs(meta)
-        alpha = torch.empty((T, H * D), dtype=torch.float32, device=self.device)
+        chunked = first is not None and self.gla_in_chunks and \
+            self.lib.raw("rb_gla_chunked_supports")(D, Dv, proj.stride(0), at["q"], at["k"], at["v"])
+        alpha = torch.empty((T, H * D), dtype=torch.float32, device=self.device)       # the decays, or their logarithms
         self.lib.call("rb_gla_decay", _ptr(alpha), _ptr(proj), proj.stride(0), at["a"], _ptr(p.a2), _ptr(p.a2_bias), T, H * D, R,
-                      float(p.tau), self._stream())
+                      float(p.tau), 1 if chunked else 0, self._stream())
         o = torch.empty((T, H * Dv), dtype=torch.float32, device=self.device)
-        self.lib.call("rb_gla_scan", _ptr(o), _ptr(proj), proj.stride(0), at["q"], at["k"], at["v"], _ptr(alpha),
-                      float(D) ** -0.5, _ptr(state["S"]), _ptr(first), _ptr(count), _ptr(meta.tok_slot), n_runs, H, D, Dv,
-                      self._stream())
+        if chunked:
+            # runs of several tokens: chunks of 32, the chain in time only from chunk to chunk
+            run_chunk0, chunk_row, chunk_len, n_chunks = self._delta_chunks(meta)
+            scratch = torch.empty((n_chunks * H * self.lib.raw("rb_gla_chunk_floats")(D),), dtype=torch.float32,
+                                  device=self.device)
+            self.lib.call("rb_gla_chunked", _ptr(o), _ptr(proj), proj.stride(0), at["q"], at["k"], at["v"], _ptr(alpha),
+                          float(D) ** -0.5, _ptr(state["S"]), _ptr(scratch), _ptr(first), _ptr(count), _ptr(run_chunk0),
+                          _ptr(chunk_row), _ptr(chunk_len), _ptr(meta.tok_slot), n_runs, n_chunks, H, D, Dv, self._stream(),
+                          launches=2)
+        else:
+            self.lib.call("rb_gla_scan", _ptr(o), _ptr(proj), proj.stride(0), at["q"], at["k"], at["v"], _ptr(alpha),
+                          float(D) ** -0.5, _ptr(state["S"]), _ptr(first), _ptr(count), _ptr(meta.tok_slot), n_runs, H, D, Dv,
+                          self._stream())
         out = torch.empty((T, H * Dv), dtype=self.dtype, device=self.device)
         self.lib.call("rb_head_norm_gate", _ptr(out), self.code, _ptr(o), _ptr(p.norm_w), _ptr(proj), proj.stride(0), F32,
                       at["g"], T, H, Dv, float(p.norm_eps), 1, 1, self._stream())

@@ -88,20 +88,22 @@ def spec_of(cfg_dict):
 
 def make_tensors(cfg_dict, seed, spread=8.0, long_memory=True):
     """Random weights, then made so that faults show: matrices are scaled up (random weights of deviation 0.02 give
-    nearly uniform attention, gates stuck at one half and a router without preferences); the gates' biases are spread;
+    nearly uniform attention, gates stuck at one half, a router without preferences and a convolution that adds
+    nothing); the gates' biases are spread;
     with ``long_memory`` the memory of a gla layer forgets slowly, so that a token far back still moves the logits."""
     t = random_tensors(spec_of(cfg_dict), seed)
     out = {}
     for name, v in t.items():
         v = v.clone()
         if name.endswith(".router") or name.endswith(".shared.sg"):
-            v = v * 3.0 * spread
+            # sums of deviation 2 whatever the width: spread scores, none so near 0 or 1 that float32 cannot tell two apart
+            v = v * (2.0 / (0.02 * v.shape[-1] ** 0.5))
         elif name.endswith(".a2.b"):
             v = v * 20.0 + (5.0 if long_memory else 0.0)          # sigmoid near one: decays near one
         elif name.endswith(".rg1.b") or name.endswith(".rg2.b"):
             v = v * 30.0
         elif ".canon" in name:
-            v = v * 1.0                                           # taps near 1 / taps, as made
+            v = v * 25.0                                          # taps of deviation one half: earlier rows count
         elif v.dim() >= 2:
             v = v * spread
         out[name] = v.to(torch.bfloat16).to(torch.float32)     # values both dtypes of the engine can hold

@@ -196,13 +196,18 @@ def test_gated_add_and_softcap():
 
 
 @pytest.mark.parametrize("H,D,Dv,R,tau", [(2, 16, 24, 8, 8.0), (1, 40, 8, 4, 1.0), (3, 8, 12, 5, 2.0), (4, 128, 64, 16, 16.0),
-                                          (2, 100, 33, 3, 4.0), (1, 300, 20, 7, 64.0), (2, 8, 130, 2, 16.0), (2, 512, 8, 9, 3.0)])
-def test_gated_linear_attention_kernels(H, D, Dv, R, tau):
+                                          (2, 100, 33, 3, 4.0), (1, 300, 20, 7, 64.0), (2, 8, 130, 2, 16.0), (2, 512, 8, 9, 3.0),
+                                          (2, 100, 36, 3, 0.5), (1, 64, 20, 4, 0.25)])
+@pytest.mark.parametrize("chunks", [True, False])
+def test_gated_linear_attention_kernels(H, D, Dv, R, tau, chunks):
     """Whole runs, portions and single tokens through the memory; key sizes that one to thirty-two lanes hold; decays
-    near one, so that the memory of the first tokens is still there at the end, and decays near zero in some channels;
-    two sequences in one step with the neighbouring slots untouched."""
+    near one, so that the memory of the first tokens is still there at the end, and decays near zero in some channels
+    (a small tau: a channel that loses everything within a few tokens of a chunk); two sequences in one step with the
+    neighbouring slots untouched.  Runs of several tokens in chunks of 32 (a run of 100 tokens ends inside its fourth
+    chunk; value sizes that fill a tile of columns and that do not) and token by token."""
     from rbitnet_b200.parts.gla import GatedLinearAttention
     ops = _ops(torch.float32)
+    ops.gla_in_chunks = chunks
     g = torch.Generator().manual_seed(H * 1000 + D)
     E, T = 32, 100
     part = GatedLinearAttention(E, H, D, Dv, R, tau, norm_eps=1e-5)
