@@ -566,6 +566,22 @@ RB_EXPORT int rb_route_select(int* ids, float* weights, const float* z, const fl
   return 0;
 }
 
+// The choice with the variants of rb_route_scored, from sums z [T, n + n_extra] that a product has left.
+RB_EXPORT int rb_route_select_scored(int* ids, float* weights, const float* z, const float* correction, int T, int n, int top,
+                                     int groups, int keep, int scoring, int n_extra, float* extra, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(n > 0 && top > 0 && top <= n && n_extra >= 0 && (n_extra == 0 || extra != nullptr),
+             "rb_route_select_scored: bad sizes outputs=%d top=%d extra=%d", n, top, n_extra);
+  RB_REQUIRE(groups <= 1 || n % groups == 0, "rb_route_select_scored: %d outputs are not %d equal groups", n, groups);
+  if (groups < 1) groups = 1;
+  const size_t smem_sel = (size_t)4 * (2 * n + 2 * groups) * sizeof(float);
+  RB_REQUIRE(smem_sel <= 48 * 1024, "rb_route_select_scored: %d router outputs are more than a block's shared memory holds", n);
+  RB_LAUNCH("route_select_kernel", (route_select_kernel), (T + 3) / 4, 128, smem_sel, stream, ids, weights, z, correction, T, n, top,
+            groups, keep, scoring, n_extra, extra);
+  RB_CHECK_LAUNCH("rb_route_select_scored");
+  return 0;
+}
+
 // Tiles of rows the padded buffer needs at most for `pairs` pairs over n_experts experts.
 RB_EXPORT int rb_routed_tiles(int pairs, int n_experts, int tile) {
   if (pairs <= 0 || tile <= 0) return 0;

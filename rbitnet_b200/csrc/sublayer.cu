@@ -18,9 +18,21 @@ __device__ __forceinline__ float sigmoid_(float v) { return 1.0f / (1.0f + expf(
 // ---------------------------------------------------------------- grouped RMS norm
 // A block per row; a warp takes the row's parts in turn (two passes over the part: the sum of squares, then the
 // values; the second pass finds the part in the SM's cache).
+__device__ __forceinline__ void store4(float* d, float a, float b, float c, float e) {
+  *reinterpret_cast<float4*>(d) = make_float4(a, b, c, e);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* d, float a, float b, float c, float e) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, e);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&lo);
+  u.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(d) = u;
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(256) rmsnorm_grouped_kernel(TO* __restrict__ out, const float* __restrict__ x,
-                                                              const float* __restrict__ w, int E, int groups, float eps) {
+                                                              const float* __restrict__ w, int E, int groups, float eps,
+                                                              int vec) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -30,6 +42,41 @@ __global__ void __launch_bounds__(256) rmsnorm_grouped_kernel(TO* __restrict__ o
   for (int g = warp; g < groups; g += nw) {
     const float* p = row + (int64_t)g * per;
     float ss = 0.f;
+    if (vec) {
+      // 16 bytes a load; a part of up to 1,024 values stays in the lane's registers between the two passes
+      float4 keep[8];
+      const int n4 = per >> 2;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = lane + 32 * u;
+        if (i < n4) {
+          keep[u] = reinterpret_cast<const float4*>(p)[i];
+          ss = fmaf(keep[u].x, keep[u].x, fmaf(keep[u].y, keep[u].y, fmaf(keep[u].z, keep[u].z, fmaf(keep[u].w, keep[u].w, ss))));
+        }
+      }
+      for (int i = lane + 256; i < n4; i += 32) {
+        const float4 v = reinterpret_cast<const float4*>(p)[i];
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+      }
+      ss = rb_warp_sum(ss);
+      const float r = 1.0f / sqrtf(ss / (float)per + eps);
+      const float4* w4 = reinterpret_cast<const float4*>(w + (int64_t)g * per);
+      TO* d = dst + (int64_t)g * per;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = lane + 32 * u;
+        if (i < n4) {
+          const float4 ww = w4[i];
+          store4(d + 4 * i, keep[u].x * r * ww.x, keep[u].y * r * ww.y, keep[u].z * r * ww.z, keep[u].w * r * ww.w);
+        }
+      }
+      for (int i = lane + 256; i < n4; i += 32) {
+        const float4 v = reinterpret_cast<const float4*>(p)[i];
+        const float4 ww = w4[i];
+        store4(d + 4 * i, v.x * r * ww.x, v.y * r * ww.y, v.z * r * ww.z, v.w * r * ww.w);
+      }
+      continue;
+    }
     for (int i = lane; i < per; i += 32) ss = fmaf(p[i], p[i], ss);
     ss = rb_warp_sum(ss);
     const float r = 1.0f / sqrtf(ss / (float)per + eps);
@@ -65,6 +112,84 @@ __global__ void input_filter_kernel(T* __restrict__ out, const T* __restrict__ h
       }
       out[(int64_t)t * C + c] = rb_from_float<T>(acc);
       if (update && K > 1) ring[((int64_t)slot * K + pos % K) * C + c] = own;
+    }
+  }
+}
+
+// The same for widths and addresses that allow 16 bytes a load and at most KM taps: a thread owns V neighbouring
+// channels, keeps their taps in registers, and takes the block's rows in turn (the rows behind a row were just read
+// by the same block and come from the SM's cache).
+template <typename T, int V> struct FilterVec;
+template <> struct FilterVec<float, 4> {
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct FilterVec<__nv_bfloat16, 8> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(b[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    uint4 a;
+    __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&a);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) b[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = a;
+  }
+};
+
+template <typename T, int V, int KM>
+__global__ void __launch_bounds__(256) input_filter_vec_kernel(T* __restrict__ out, const T* __restrict__ h,
+                                                               const float* __restrict__ taps, float* __restrict__ ring,
+                                                               const int* __restrict__ tok_first,
+                                                               const int* __restrict__ tok_slot,
+                                                               const int* __restrict__ tok_pos, int n_tokens, int C, int K,
+                                                               int update, int per_block) {
+  rb_pdl_launch_dependents();
+  const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+  if (c0 >= C) return;
+  float w[KM][V];                                  // w[d][v]: the tap on the row d back
+#pragma unroll
+  for (int d = 0; d < KM; ++d)
+#pragma unroll
+    for (int v = 0; v < V; ++v) w[d][v] = d < K ? taps[(int64_t)(c0 + v) * K + (K - 1 - d)] : 0.f;
+  rb_pdl_wait();
+  for (int t = blockIdx.x * per_block; t < min(n_tokens, (int)(blockIdx.x + 1) * per_block); ++t) {
+    const int first = tok_first != nullptr ? tok_first[t] : t;
+    const int slot = tok_slot[t], pos = tok_pos[t];
+    const int j = t - first;
+    float own[V], acc[V];
+    FilterVec<T, V>::load(h + (int64_t)t * C + c0, own);
+#pragma unroll
+    for (int v = 0; v < V; ++v) acc[v] = fmaf(w[0][v], own[v], own[v]);
+#pragma unroll
+    for (int d = 1; d < KM; ++d) {
+      if (d >= K || (d > j && pos - d < 0)) continue;
+      float x[V];
+      if (d <= j) {
+        FilterVec<T, V>::load(h + (int64_t)(t - d) * C + c0, x);
+      } else {
+        const float* r = ring + ((int64_t)slot * K + (pos - d) % K) * C + c0;
+#pragma unroll
+        for (int v = 0; v < V; v += 4) FilterVec<float, 4>::load(r + v, x + v);
+      }
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[v] = fmaf(w[d][v], x[v], acc[v]);
+    }
+    FilterVec<T, V>::store(out + (int64_t)t * C + c0, acc);
+    if (update && K > 1) {
+      float* r = ring + ((int64_t)slot * K + pos % K) * C + c0;
+#pragma unroll
+      for (int v = 0; v < V; v += 4) FilterVec<float, 4>::store(r + v, own + v);
     }
   }
 }
@@ -114,10 +239,11 @@ RB_EXPORT int rb_rmsnorm_grouped(void* out, int out_dtype, const float* x, const
   if (T == 0) return 0;
   RB_REQUIRE(groups >= 1 && E > 0 && E % groups == 0, "rb_rmsnorm_grouped: a row of %d values is not %d equal parts", E, groups);
   const int threads = groups >= 8 ? 256 : 32 * groups;
+  const int vec = (E / groups) % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0;
   if (out_dtype == RB_F32)
-    RB_LAUNCH("rmsnorm_grouped_kernel", (rmsnorm_grouped_kernel<float>), T, threads, 0, stream, (float*)out, x, w, E, groups, eps);
+    RB_LAUNCH("rmsnorm_grouped_kernel", (rmsnorm_grouped_kernel<float>), T, threads, 0, stream, (float*)out, x, w, E, groups, eps, vec);
   else if (out_dtype == RB_BF16)
-    RB_LAUNCH("rmsnorm_grouped_kernel", (rmsnorm_grouped_kernel<__nv_bfloat16>), T, threads, 0, stream, (__nv_bfloat16*)out, x, w, E, groups, eps);
+    RB_LAUNCH("rmsnorm_grouped_kernel", (rmsnorm_grouped_kernel<__nv_bfloat16>), T, threads, 0, stream, (__nv_bfloat16*)out, x, w, E, groups, eps, vec);
   else
     RB_FAIL("rb_rmsnorm_grouped: unknown dtype %d", out_dtype);
   RB_CHECK_LAUNCH("rb_rmsnorm_grouped");
@@ -130,12 +256,30 @@ RB_EXPORT int rb_input_filter(void* out, const void* h, int dtype, const float* 
                               const int* tok_slot, const int* tok_pos, int T, int C, int K, cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(C > 0 && K >= 1, "rb_input_filter: bad sizes C=%d K=%d", C, K);
+  const int update = tok_first == nullptr ? 1 : 0;
+  {
+    constexpr int KM = 4;
+    const int V = dtype == RB_F32 ? 4 : 8;
+    const bool aligned = (uintptr_t)out % 16 == 0 && (uintptr_t)h % 16 == 0 && (ring == nullptr || (uintptr_t)ring % 16 == 0);
+    if (K <= KM && C % V == 0 && aligned && (dtype == RB_F32 || dtype == RB_BF16)) {
+      const int lanes = C / V;
+      const int threads = lanes >= 256 ? 256 : ((lanes + 31) / 32) * 32;
+      const int per_block = T >= 512 ? 4 : 1;
+      const dim3 grid((T + per_block - 1) / per_block, (lanes + threads - 1) / threads);
+      RB_REQUIRE(grid.y <= 65535, "rb_input_filter: %d channels are too many for one launch", C);
+      if (dtype == RB_F32)
+        RB_LAUNCH("input_filter_vec_kernel", (input_filter_vec_kernel<float, 4, KM>), grid, threads, 0, stream, (float*)out, (const float*)h, taps, ring, tok_first, tok_slot, tok_pos, T, C, K, update, per_block);
+      else
+        RB_LAUNCH("input_filter_vec_kernel", (input_filter_vec_kernel<__nv_bfloat16, 8, KM>), grid, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)h, taps, ring, tok_first, tok_slot, tok_pos, T, C, K, update, per_block);
+      RB_CHECK_LAUNCH("rb_input_filter");
+      return 0;
+    }
+  }
   const int threads = 128;
   int by = (C + threads - 1) / threads;
   if (by > 64) by = 64;
   const int per_block = T >= 512 ? 8 : 1;
   const dim3 grid((T + per_block - 1) / per_block, by);
-  const int update = tok_first == nullptr ? 1 : 0;
   if (dtype == RB_F32)
     RB_LAUNCH("input_filter_kernel", (input_filter_kernel<float>), grid, threads, 0, stream, (float*)out, (const float*)h, taps, ring, tok_first, tok_slot, tok_pos, T, C, K, update, per_block);
   else if (dtype == RB_BF16)

@@ -42,6 +42,7 @@ _SIGNATURES = {
     "rb_add_rows": [P, P, ctypes.c_longlong, P],
     "rb_route": [P, P, P, L, I, P, P, I, I, I, I, I, I, P, P],
     "rb_route_select": [P, P, P, P, I, I, I, I, I, P],
+    "rb_route_select_scored": [P, P, P, P, I, I, I, I, I, I, I, P, P],
     "rb_routed_tiles": [I, I, I],
     "rb_routed_plan": [P, P, P, P, I, I, I, I, I, P],
     "rb_routed_gather": [P, P, L, I, P, I, I, P],

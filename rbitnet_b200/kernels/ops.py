@@ -884,6 +884,13 @@ class CudaOps:
         ids = torch.empty((T, top), dtype=torch.int32, device=self.device)
         weights = torch.empty((T, top), dtype=torch.float32, device=self.device)
         extra = torch.empty((T, extra_rows), dtype=torch.float32, device=self.device) if extra_rows else None
+        if T >= 64 and router_tc is not None and self._tensor_core_ok(h, router_tc.w):
+            # many tokens: the sums (outputs and extra rows) on the tensor cores, then the choice
+            z = self.linear(h, router_tc, out_dtype=torch.float32)
+            self.lib.call("rb_route_select_scored", _ptr(ids), _ptr(weights), _ptr(z), _ptr(correction), T, n, int(top),
+                          int(groups), int(keep), {"softmax": 0, "sigmoid": 1}[scoring], int(extra_rows), _ptr(extra),
+                          self._stream())
+            return ids, weights, extra
         z = torch.empty((T, n + extra_rows), dtype=torch.float32, device=self.device) if T >= 64 else None
         self.lib.call("rb_route_scored", _ptr(ids), _ptr(weights), _ptr(h), h.stride(0), self.code, _ptr(router),
                       _ptr(correction), T, K, n, int(top), int(groups), int(keep), _ptr(z),

@@ -155,23 +155,23 @@ def test_norm_in_groups(T, E, groups):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("C,K", [(64, 3), (100, 1), (33, 4), (512, 2), (8, 7)])
-def test_input_filter(dtype, C, K):
+@pytest.mark.parametrize("C,K,T", [(64, 3, 50), (100, 1, 50), (33, 4, 50), (512, 2, 50), (8, 7, 50), (256, 4, 601)])
+def test_input_filter(dtype, C, K, T):
     """Whole runs, portions shorter than the taps and single rows through the ring; two sequences in one step; a slot
-    whose ring holds another sequence's rows counts as empty at position 0."""
+    whose ring holds another sequence's rows counts as empty at position 0.  Widths that allow 16 bytes a load and
+    widths that do not; more taps than the kernel of wide loads keeps; steps of so many rows that a block takes several."""
     from rbitnet_b200.parts.sublayer import CausalTapsFilter
     ops = _ops(dtype)
     g = torch.Generator().manual_seed(C + K)
     part = CausalTapsFilter(C, K)
     taps = torch.randn(C, K, generator=g, dtype=torch.float64)
     part.bind({"taps": taps.float().cuda()}, ops)
-    T = 50
     ha = torch.randn(T, C, generator=g).to(torch.bfloat16).double()
     hb = torch.randn(T, C, generator=g).to(torch.bfloat16).double()
     want_a, want_b = plain.canon(ha, taps), plain.canon(hb, taps)
     tol = 1e-5 if dtype == torch.float32 else 1e-2
     need = part.state_need()
-    for cuts in ([0, T], [0, 1, 2, 3, 4, 6, 9, 30, T], list(range(T + 1))):
+    for cuts in ([0, T], [0, 1, 2, 3, 4, 6, 9, 30, T], list(range(T + 1)) if T <= 100 else [0, 299, T]):
         ring = torch.full((4, *need.shape), 7.0, device="cuda") if need is not None else None      # stale rows
         outs_a, outs_b = [], []
         for a, b in zip(cuts[:-1], cuts[1:]):
@@ -325,6 +325,29 @@ def test_router_with_sigmoid_scores(n, top, T, K, extra):
         assert rel_err(gate.cpu(), h @ router[n:].T) <= 1e-5
     else:
         assert gate is None
+
+
+@pytest.mark.parametrize("n,top,T,K,extra", [(16, 4, 200, 64, 1), (5, 1, 64, 128, 0), (33, 8, 700, 256, 1), (6, 2, 63, 64, 1)])
+def test_router_sums_on_the_tensor_cores(n, top, T, K, extra):
+    """In bfloat16 mode a router whose float32 values are bfloat16 values has its sums (outputs and extra rows) made by
+    the tensor-core product from 64 tokens on; the choice and the weights are those of the plain sums."""
+    ops = _ops(torch.bfloat16)
+    g = torch.Generator().manual_seed(n * 7 + top)
+    h = torch.randn(T, K, generator=g).to(torch.bfloat16).double()
+    router = (torch.randn(n + extra, K, generator=g) * 0.3).to(torch.bfloat16).double()
+    tc = ops.prepare_router(router.float().cuda())
+    assert tc is not None
+    ids, weights, gate = ops.route_scored(h.to(torch.bfloat16).cuda(), router.float().cuda(), None, top, 0, 0,
+                                          scoring="sigmoid", extra_rows=extra, router_tc=tc)
+    s = torch.sigmoid(h @ router[:n].T)
+    want = torch.topk(s, top, dim=-1)
+    ids, weights = ids.cpu().long(), weights.cpu().double()
+    for t in range(T):
+        assert sorted(ids[t].tolist()) == sorted(want.indices[t].tolist()), t
+        assert float((weights[t].sort().values - want.values[t].sort().values).abs().max()) <= 3e-6
+    if extra:
+        assert rel_err(gate.cpu(), h @ router[n:].T) <= 1e-5
+    ops.check_errors()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
