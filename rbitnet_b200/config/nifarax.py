@@ -82,8 +82,11 @@ class NifaraxConfig(ModelConfig):
             if src is not None:
                 if not isinstance(src, int) or not 0 <= src < len(self.layers) or src == i:
                     raise ConfigError(f"config.json: {where}.weights_of must name another layer")
-                if self.layers[src].get("weights_of") is not None:
-                    raise ConfigError(f"config.json: {where}.weights_of names layer {src}, which has no tensors of its own")
+                hops = 0
+                while isinstance(self.layers[src].get("weights_of"), int) and 0 <= self.layers[src]["weights_of"] < len(self.layers):
+                    src, hops = self.layers[src]["weights_of"], hops + 1      # a layer that itself uses another's tensors
+                    if hops > len(self.layers):
+                        raise ConfigError(f"config.json: {where}.weights_of leads back to itself")
                 if self.layers[src]["type"] != kind:
                     raise ConfigError(f"config.json: {where} uses the tensors of layer {src}, which is of another type")
             mlp = layer.get("mlp")
@@ -120,7 +123,10 @@ class NifaraxConfig(ModelConfig):
                 layer["mixer"] = dict(layer["mixer"], decay_rank=int(shape[0]))
         for layer in self.layers:
             if layer["type"] == "gla" and layer.get("weights_of") is not None:
-                rank = self.layers[layer["weights_of"]]["mixer"].get("decay_rank")
+                src = layer["weights_of"]
+                while self.layers[src].get("weights_of") is not None:
+                    src = self.layers[src]["weights_of"]
+                rank = self.layers[src]["mixer"].get("decay_rank")
                 if rank is not None:
                     layer["mixer"] = dict(layer["mixer"], decay_rank=rank)
 

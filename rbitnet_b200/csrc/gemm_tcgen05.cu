@@ -1143,8 +1143,10 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   const StoreOptions store = t_store;
   t_store = StoreOptions();
   if (n_tokens == 0 || n_out == 0) return 0;
-  RB_REQUIRE((store.square_relu == 0 && store.tile_group == nullptr) || epilogue == EPI_STORE,
-             "rb_gemm_tc: a squared activation or grouped rows with epilogue %d (only a stored product has them)", epilogue);
+  RB_REQUIRE((store.square_relu == 0 && store.tile_group == nullptr) || epilogue == EPI_STORE ||
+                 (store.square_relu == 0 && epilogue == EPI_GATED),
+             "rb_gemm_tc: a squared activation or grouped rows with epilogue %d (a stored product has them; a gated one grouped rows)",
+             epilogue);
   RB_REQUIRE(store.tile_group == nullptr || (splits == 1 && token_tile > 0 && w_rows % n_out == 0),
              "rb_gemm_tc: grouped rows want K whole, a given token tile and whole groups (splits %d, tile %d, %d rows of %d)",
              splits, token_tile, w_rows, n_out);

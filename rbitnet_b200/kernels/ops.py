@@ -870,6 +870,10 @@ class CudaOps:
     def prepare_expert_gate_up(self, gates: List[torch.Tensor], ups: List[torch.Tensor]) -> ExpertGateUp:
         """The gated experts' first matrices, one expert below the other, an expert's rows [gate | up]."""
         inner, K = gates[0].shape
+        if self.dtype == torch.bfloat16 and K % 8 == 0:
+            # every expert in the layout of the tensor-core gated product (16 gate rows, then their 16 up rows)
+            each = [self.prepare_gate_up(g, u) for g, u in zip(gates, ups)]
+            return ExpertGateUp(torch.cat([e.w for e in each], dim=0).contiguous(), inner, K, each[0].w.shape[0], 16)
         w = torch.cat([torch.cat([self.to_compute(g), self.to_compute(u)], dim=0) for g, u in zip(gates, ups)], dim=0)
         return ExpertGateUp(w.contiguous(), inner, K, 2 * inner, 0)
 
@@ -978,17 +982,25 @@ class CudaOps:
             if act is not None:
                 # gated experts: the grouped product leaves float32 [gate | up] rows, a kernel makes the inner rows
                 per = w_up.rows
-                gu = torch.empty((rows, per), dtype=torch.float32, device=self.device)
                 tc = self._routed_on_tensor_cores(inner, E)
-                if tc:
+                fused = tc and w_up.block == 16 and self.fuse_gated_act
+                gu = None if fused else torch.empty((rows, per), dtype=torch.float32, device=self.device)
+                if fused:
+                    # the activation in the grouped product's epilogue: the inner rows leave it in bfloat16
+                    self.lib.call("rb_gemm_tc_gated_act", float(act[0]), float(act[1]), float(act[2]), launches=0)
+                    self.lib.call("rb_gemm_tc_grouped", _ptr(tile_group), launches=0)
+                    self.lib.call("rb_gemm_tc", _ptr(mid), mid.stride(0), self.code, _ptr(xp), xp.stride(0), rows, _ptr(w_up.w),
+                                  w_up.w.stride(0), n_experts * per, per, E, 3, inner, 1, tile, 1.0, self._stream())
+                elif tc:
                     self.lib.call("rb_gemm_tc_grouped", _ptr(tile_group), launches=0)
                     self.lib.call("rb_gemm_tc", _ptr(gu), gu.stride(0), F32, _ptr(xp), xp.stride(0), rows, _ptr(w_up.w),
                                   w_up.w.stride(0), n_experts * per, per, E, 0, 0, 1, tile, 1.0, self._stream())
                 else:
                     self.lib.call("rb_gemm_grouped_simple", _ptr(gu), gu.stride(0), F32, _ptr(xp), xp.stride(0), _ptr(w_up.w),
                                   w_up.w.stride(0), self.code, _ptr(tile_group), rows, per, E, 0, self._stream())
-                self.lib.call("rb_gated_act", _ptr(mid), _ptr(gu), self.code, F32, rows, inner, gu.stride(0), w_up.block,
-                              float(act[0]), float(act[1]), float(act[2]), self._stream())
+                if not fused:
+                    self.lib.call("rb_gated_act", _ptr(mid), _ptr(gu), self.code, F32, rows, inner, gu.stride(0), w_up.block,
+                                  float(act[0]), float(act[1]), float(act[2]), self._stream())
                 if tc:
                     self.lib.call("rb_gemm_tc_grouped", _ptr(tile_group), launches=0)
                     self.lib.call("rb_gemm_tc", _ptr(y), y.stride(0), F32, _ptr(mid), mid.stride(0), rows, _ptr(w_down.w),

@@ -78,8 +78,17 @@ def build_nifarax_spec(cfg: NifaraxConfig) -> ModelSpec:
                     names[f"{part_name}.{key}"] = f"l{i}.{prefix}.{key}"
         block_of[i] = len(layers)
         layers.append(BlockSpec(parts=parts, names=names, arrangement="pre_norm_gated"))
-    schedule = [ScheduleEntry(block_of[layer["weights_of"] if layer.get("weights_of") is not None else i])
-                for i, layer in enumerate(cfg.layers)]
+    def stored(i: int) -> int:
+        """The layer whose tensors layer i uses (itself, or the end of a chain of ``weights_of``)."""
+        seen = set()
+        while cfg.layers[i].get("weights_of") is not None:
+            if i in seen:
+                raise ConfigError(f"config.json: layers[{i}].weights_of leads back to itself")
+            seen.add(i)
+            i = int(cfg.layers[i]["weights_of"])
+        return i
+
+    schedule = [ScheduleEntry(block_of[stored(i)]) for i in range(len(cfg.layers))]
     return ModelSpec(
         width=cfg.width, vocab_size=cfg.vocab, embedding_name="embed", layers=layers, schedule=schedule,
         final_norm=norm, final_norm_names={"weight": "final.norm"}, head_name=None,

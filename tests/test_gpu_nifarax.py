@@ -354,12 +354,17 @@ def test_router_sums_on_the_tensor_cores(n, top, T, K, extra):
 @pytest.mark.parametrize("T,E,F,n,top,shared", [(1, 64, 40, 6, 2, (48, 1.0)), (3, 64, 40, 6, 6, None), (70, 64, 24, 3, 1, (24, 2.5)),
                                                 (300, 128, 72, 16, 4, (256, 0.7)), (45, 100, 36, 4, 2, (20, 1.0)),
                                                 (2500, 64, 32, 5, 2, None), (9, 64, 44, 2, 1, (8, 1.0))])
-def test_experts_weighted_on_their_inputs(dtype, T, E, F, n, top, shared):
+@pytest.mark.parametrize("fused", [True, False])
+def test_experts_weighted_on_their_inputs(dtype, T, E, F, n, top, shared, fused):
     """Few pairs and many, tiles of every size, experts without any token, a width and an inner size that the
     tensor-core products refuse, with and without the shared expert.  The weight multiplies what the expert reads: with
-    limits that bite, that differs from weighing its result."""
+    limits that bite, that differs from weighing its result.  The activation in the grouped product's epilogue and as
+    a kernel of its own."""
     from rbitnet_b200.parts.feed_forward import RoutedExperts
+    if dtype == torch.float32 and not fused:
+        pytest.skip("float32 has the one form")
     ops = _ops(dtype)
+    ops.fuse_gated_act = fused
     g = torch.Generator().manual_seed(T + E)
     part = RoutedExperts(E, F, n, top, correction=False, activation="swish_limited", scoring="sigmoid", weight_on="input",
                          limit=0.8, shared={"inner": shared[0], "limit": shared[1]} if shared else None)
