@@ -22,21 +22,39 @@ constexpr int GLA_R = 16;        // channels a lane holds
 
 __device__ __forceinline__ float softplus_(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
-__global__ void gla_decay_kernel(float* __restrict__ alpha, const float* __restrict__ rows, int64_t ld, int a_off,
-                                 const float* __restrict__ A2, const float* __restrict__ bias, int T, int C, int rank,
-                                 float inv_tau, int as_log) {
+// A block takes GLA_DT rows and 128 channels at a time: a channel's row of A2 is read once for all of them.
+constexpr int GLA_DT = 8;
+__global__ void __launch_bounds__(128) gla_decay_kernel(float* __restrict__ alpha, const float* __restrict__ rows, int64_t ld,
+                                                        int a_off, const float* __restrict__ A2,
+                                                        const float* __restrict__ bias, int T, int C, int rank,
+                                                        float inv_tau, int as_log) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
-  const int t = blockIdx.x;
-  extern __shared__ float s_low[];                 // A1 h of this row
-  for (int r = threadIdx.x; r < rank; r += blockDim.x) s_low[r] = rows[(int64_t)t * ld + a_off + r];
+  const int t0 = blockIdx.x * GLA_DT, nt = min(GLA_DT, T - t0);
+  extern __shared__ float s_low[];                 // A1 h of these rows: [GLA_DT][rank], zeros for rows beyond the last
+  for (int e = threadIdx.x; e < GLA_DT * rank; e += blockDim.x) {
+    const int i = e / rank, r = e - i * rank;
+    s_low[e] = i < nt ? rows[(int64_t)(t0 + i) * ld + a_off + r] : 0.f;
+  }
   __syncthreads();
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
-    float z = bias != nullptr ? bias[c] : 0.f;
+    float z[GLA_DT];
+    const float b = bias != nullptr ? bias[c] : 0.f;
+#pragma unroll
+    for (int i = 0; i < GLA_DT; ++i) z[i] = b;
     const float* w = A2 + (int64_t)c * rank;
-    for (int r = 0; r < rank; ++r) z = fmaf(w[r], s_low[r], z);
-    const float lg = -softplus_(-z) * inv_tau;                 // log alpha
-    alpha[(int64_t)t * C + c] = as_log ? lg : expf(lg);
+    for (int r = 0; r < rank; ++r) {
+      const float wr = w[r];
+#pragma unroll
+      for (int i = 0; i < GLA_DT; ++i) z[i] = fmaf(wr, s_low[i * rank + r], z[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < GLA_DT; ++i) {
+      if (i < nt) {
+        const float lg = -softplus_(-z[i]) * inv_tau;            // log alpha
+        alpha[(int64_t)(t0 + i) * C + c] = as_log ? lg : expf(lg);
+      }
+    }
   }
 }
 
@@ -224,7 +242,8 @@ __global__ void __launch_bounds__(128) gla_chunk_prepare_kernel(float* __restric
 }
 
 // grid (runs, H, tiles of 16 value columns), 256 threads.  Shared memory: two buffers of a chunk's item (as the first
-// kernel left it) and the tile's values [32][16], filled a chunk ahead with cp.async; the memory's tile S [16][D + 4].
+// kernel left it) and the tile's values [32][16], filled a chunk ahead with cp.async; the memory's tile S [16][D + 4]
+// twice: a chunk reads one and writes the other, so that its read-out and its update need no barrier between them.
 __global__ void __launch_bounds__(GSCAN_NT) gla_chunk_scan_kernel(
     float* __restrict__ o, const float* __restrict__ scratch, const float* __restrict__ rows, int64_t ld, int v_off,
     float* __restrict__ state, const int* __restrict__ seq_first, const int* __restrict__ seq_count,
@@ -234,7 +253,8 @@ __global__ void __launch_bounds__(GSCAN_NT) gla_chunk_scan_kernel(
   const int item_floats = gla_item_floats(D);
   const int per_buf = item_floats + GCH * GCT;
   const int SS = D + 4;
-  float* Ss = s_gscan + 2 * per_buf;   // [16][D + 4]
+  float* Sa = s_gscan + 2 * per_buf;    // [16][D + 4]: the memory as this chunk finds it
+  float* Sb = Sa + GCT * SS;            // the memory as this chunk leaves it (the two change places after every chunk)
   const int run = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * GCT;
   const int tid = threadIdx.x;
   rb_pdl_wait();
@@ -258,20 +278,21 @@ __global__ void __launch_bounds__(GSCAN_NT) gla_chunk_scan_kernel(
   float* mine = state + (((int64_t)slot * H + h) * Dv + col0) * D;      // [column][D]
   for (int i = tid; i < D * GCT; i += GSCAN_NT) {
     const int cc = i / D, d = i - cc * D;
-    Ss[cc * SS + d] = col0 + cc < Dv ? mine[(int64_t)cc * D + d] : 0.f;
+    Sa[cc * SS + d] = col0 + cc < Dv ? mine[(int64_t)cc * D + d] : 0.f;
   }
   const int c = tid & 15, g = tid >> 4;              // read-out: column c, rows g and g + 16
   const int dq = (tid & 31) << 2, cp = (tid >> 5) << 1;   // update: channels dq .. dq + 3 of columns cp and cp + 1
   for (int ci = 0, buf = 0; ci < n_chunks; ++ci, buf ^= 1) {
     const int row0 = first + ci * GCH, m = min(GCH, n - ci * GCH);
+    cp_async_wait<0>();
+    __syncthreads();                  // this chunk's copies have landed, the memory the last chunk left is whole, and
+                                      // nobody reads the other buffer any more: the one barrier of a chunk
     if (ci + 1 < n_chunks) {
-      copy_chunk(ci + 1, buf ^ 1);
+      copy_chunk(ci + 1, buf ^ 1);    // lands while this chunk is multiplied
       cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
     }
-    __syncthreads();                  // this chunk's copies have landed; S is in place
+    const float* Ss = (ci & 1) ? Sb : Sa;
+    float* Sn = (ci & 1) ? Sa : Sb;
     const float* Qt = s_gscan + (size_t)buf * per_buf;
     const float* Kt = Qt + GCH * D;
     const float* Ms = Kt + GCH * D;
@@ -289,19 +310,23 @@ __global__ void __launch_bounds__(GSCAN_NT) gla_chunk_scan_kernel(
         acc0 = fmaf(a4.x, s4.x, fmaf(a4.y, s4.y, fmaf(a4.z, s4.z, fmaf(a4.w, s4.w, acc0))));
         acc1 = fmaf(b4.x, s4.x, fmaf(b4.y, s4.y, fmaf(b4.z, s4.z, fmaf(b4.w, s4.w, acc1))));
       }
-      const float* m0 = Ms + g * GCH;
-      const float* m1 = Ms + (g + 16) * GCH;
-      for (int j = 0; j <= g + 16; ++j) {
-        const float v = Vs[j * GCT + c];
-        if (j <= g) acc0 = fmaf(m0[j], v, acc0);
-        acc1 = fmaf(m1[j], v, acc1);
+      // M is zero above its diagonal, so both rows take all 32 columns: a loop of fixed length whose loads run ahead
+      const float4* m0 = reinterpret_cast<const float4*>(Ms + g * GCH);
+      const float4* m1 = reinterpret_cast<const float4*>(Ms + (g + 16) * GCH);
+#pragma unroll
+      for (int j4 = 0; j4 < GCH / 4; ++j4) {
+        const float4 a4 = m0[j4], b4 = m1[j4];
+        const float v0 = Vs[(4 * j4 + 0) * GCT + c], v1 = Vs[(4 * j4 + 1) * GCT + c];
+        const float v2 = Vs[(4 * j4 + 2) * GCT + c], v3 = Vs[(4 * j4 + 3) * GCT + c];
+        acc0 = fmaf(a4.x, v0, fmaf(a4.y, v1, fmaf(a4.z, v2, fmaf(a4.w, v3, acc0))));
+        acc1 = fmaf(b4.x, v0, fmaf(b4.y, v1, fmaf(b4.z, v2, fmaf(b4.w, v3, acc1))));
       }
       if (col0 + c < Dv) {
         if (g < m) o[((int64_t)(row0 + g) * H + h) * Dv + col0 + c] = acc0;
         if (g + 16 < m) o[((int64_t)(row0 + g + 16) * H + h) * Dv + col0 + c] = acc1;
       }
     }
-    __syncthreads();                  // every read of the old S is done
+    // the memory moves on into the other buffer, so that no thread waits here for the read-outs of the others
     if (dq < D) {
       float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
 #pragma unroll 8
@@ -312,19 +337,21 @@ __global__ void __launch_bounds__(GSCAN_NT) gla_chunk_scan_kernel(
         a1.x = fmaf(k4.x, v2.y, a1.x); a1.y = fmaf(k4.y, v2.y, a1.y); a1.z = fmaf(k4.z, v2.y, a1.z); a1.w = fmaf(k4.w, v2.y, a1.w);
       }
       const float4 e4 = *reinterpret_cast<const float4*>(Es + dq);
-      float4* s0 = reinterpret_cast<float4*>(Ss + cp * SS + dq);
-      float4* s1 = reinterpret_cast<float4*>(Ss + (cp + 1) * SS + dq);
-      float4 x = *s0, y = *s1;
+      float4 x = *reinterpret_cast<const float4*>(Ss + cp * SS + dq);
+      float4 y = *reinterpret_cast<const float4*>(Ss + (cp + 1) * SS + dq);
+      float4* s0 = reinterpret_cast<float4*>(Sn + cp * SS + dq);
+      float4* s1 = reinterpret_cast<float4*>(Sn + (cp + 1) * SS + dq);
       x.x = fmaf(e4.x, x.x, a0.x); x.y = fmaf(e4.y, x.y, a0.y); x.z = fmaf(e4.z, x.z, a0.z); x.w = fmaf(e4.w, x.w, a0.w);
       y.x = fmaf(e4.x, y.x, a1.x); y.y = fmaf(e4.y, y.y, a1.y); y.z = fmaf(e4.z, y.z, a1.z); y.w = fmaf(e4.w, y.w, a1.w);
       *s0 = x;
       *s1 = y;
     }
-    __syncthreads();                  // before the copies of the chunk after the next overwrite this buffer, and the read-out takes the new S
   }
+  __syncthreads();
+  const float* Se = (n_chunks & 1) ? Sb : Sa;
   for (int i = tid; i < D * GCT; i += GSCAN_NT) {
     const int cc = i / D, d = i - cc * D;
-    if (col0 + cc < Dv) mine[(int64_t)cc * D + d] = Ss[cc * SS + d];
+    if (col0 + cc < Dv) mine[(int64_t)cc * D + d] = Se[cc * SS + d];
   }
 }
 
@@ -336,11 +363,11 @@ RB_EXPORT int rb_gla_decay(float* alpha, const float* rows, int64_t ld, int a_of
                            int C, int rank, float tau, int as_log, cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(C > 0 && rank > 0 && tau > 0.f, "rb_gla_decay: bad sizes C=%d rank=%d tau=%g", C, rank, (double)tau);
-  RB_REQUIRE((size_t)rank * sizeof(float) <= 48 * 1024, "rb_gla_decay: a rank of %d is more than a block's shared memory holds", rank);
+  RB_REQUIRE((size_t)GLA_DT * rank * sizeof(float) <= 48 * 1024, "rb_gla_decay: a rank of %d is more than a block's shared memory holds", rank);
   int by = (C + 127) / 128;
   if (by > 32) by = 32;
-  RB_LAUNCH("gla_decay_kernel", (gla_decay_kernel), dim3(T, by), 128, (size_t)rank * sizeof(float), stream, alpha, rows, ld,
-            a_off, A2, bias, T, C, rank, 1.0f / tau, as_log);
+  RB_LAUNCH("gla_decay_kernel", (gla_decay_kernel), dim3((T + GLA_DT - 1) / GLA_DT, by), 128, (size_t)GLA_DT * rank * sizeof(float),
+            stream, alpha, rows, ld, a_off, A2, bias, T, C, rank, 1.0f / tau, as_log);
   RB_CHECK_LAUNCH("rb_gla_decay");
   return 0;
 }
@@ -390,7 +417,7 @@ RB_EXPORT int rb_gla_chunked(float* o, const float* rows, int64_t ld, int q_off,
                  (uintptr_t)scratch % 16 == 0 && (uintptr_t)log_alpha % 16 == 0,
              "rb_gla_chunked: bad sizes H=%d D=%d Dv=%d", H, D, Dv);
   const size_t smem_a = (size_t)(3 * GCH * (D + 4)) * sizeof(float);
-  const size_t smem_b = (size_t)(2 * (gla_item_floats(D) + GCH * GCT) + GCT * (D + 4)) * sizeof(float);
+  const size_t smem_b = (size_t)(2 * (gla_item_floats(D) + GCH * GCT) + 2 * GCT * (D + 4)) * sizeof(float);
   static RbOncePerDevice configured;
   if (configured.first()) {
     RB_CUDA(cudaFuncSetAttribute(gla_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
