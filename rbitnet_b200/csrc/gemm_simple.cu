@@ -139,7 +139,57 @@ __global__ void __launch_bounds__(256) gemm_simple_large_kernel(TC* __restrict__
   }
 }
 
+// Few rows (a decode step) times one matrix per head: a warp makes one output of one head for up to eight rows at a
+// time, its lanes sharing K, so that the head's matrix is read once and 8 heads x N / 8 blocks are at work instead of
+// a few tiles.  float32 sums (a lane's share in ascending order, then the lanes' shares added up).
+constexpr int FEW_ROWS = 8;
+template <typename TA, typename TC>
+__global__ void __launch_bounds__(256) per_head_few_rows_kernel(TC* __restrict__ C, int64_t ldc, const TA* __restrict__ A,
+                                                               int64_t lda, const TA* __restrict__ W, int M, int N, int K) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, n = blockIdx.x * 8 + warp;
+  if (n >= N) return;
+  const TA* w = W + ((int64_t)h * N + n) * K;
+  const TA* a = A + (int64_t)h * K;
+  for (int m0 = 0; m0 < M; m0 += FEW_ROWS) {
+    float acc[FEW_ROWS];
+#pragma unroll
+    for (int i = 0; i < FEW_ROWS; ++i) acc[i] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const float wv = rb_to_float<TA>(w[k]);
+#pragma unroll
+      for (int i = 0; i < FEW_ROWS; ++i)
+        if (m0 + i < M) acc[i] = fmaf(rb_to_float<TA>(a[(int64_t)(m0 + i) * lda + k]), wv, acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < FEW_ROWS; ++i) {
+      const float v = rb_warp_sum(acc[i]);
+      if (lane == 0 && m0 + i < M) C[(int64_t)(m0 + i) * ldc + (int64_t)h * N + n] = rb_from_float<TC>(v);
+    }
+  }
+}
+
 }  // namespace
+
+// C[m, h * N + n] = sum_k A[m, h * K + k] * W[h, n, k] for few rows m (any number is right; up to 16 is what it is for).
+RB_EXPORT int rb_per_head_few_rows(void* C, int64_t ldc, int c_dtype, const void* A, int64_t lda, const void* W, int a_dtype,
+                                   int M, int H, int N, int K, cudaStream_t stream) {
+  if (M == 0 || N == 0 || H == 0) return 0;
+  RB_REQUIRE(M > 0 && N > 0 && K > 0 && H > 0 && H <= 65535, "rb_per_head_few_rows: bad sizes M=%d H=%d N=%d K=%d", M, H, N, K);
+  const dim3 grid((N + 7) / 8, H);
+#define LAUNCH(TA, TC)                                                                                                  \
+  RB_LAUNCH("per_head_few_rows_kernel", (per_head_few_rows_kernel<TA, TC>), grid, 256, 0, stream, (TC*)C, ldc, (const TA*)A, \
+            lda, (const TA*)W, M, N, K)
+  if (a_dtype == RB_F32 && c_dtype == RB_F32) LAUNCH(float, float);
+  else if (a_dtype == RB_BF16 && c_dtype == RB_F32) LAUNCH(__nv_bfloat16, float);
+  else if (a_dtype == RB_BF16 && c_dtype == RB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else RB_FAIL("rb_per_head_few_rows: unsupported dtypes a=%d c=%d", a_dtype, c_dtype);
+#undef LAUNCH
+  RB_CHECK_LAUNCH("rb_per_head_few_rows");
+  return 0;
+}
 
 // a_dtype: dtype of A and W; c_dtype: dtype of C.  accumulate: C += instead of C =.
 // alpha multiplies the finished sum (1.0 leaves it as it is).

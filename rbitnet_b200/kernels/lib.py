@@ -22,6 +22,7 @@ _SIGNATURES = {
     "rb_gather_rows": [P, P, P, I, I, P],
     "rb_gemm_simple": [P, L, I, P, L, P, L, I, I, I, I, I, F, P],
     "rb_gemm_simple_batched": [P, L, I, P, L, P, L, I, I, I, I, I, F, I, L, L, L, P],
+    "rb_per_head_few_rows": [P, L, I, P, L, P, I, I, I, I, I, P],
     "rb_stream_step": [P, I, I, I, P, P, I, P, P, P, P, F, P, I, P, P],
     "rb_streams_expand": [P, P, I, I, I, P],
     "rb_streams_sum": [P, P, I, I, I, P],

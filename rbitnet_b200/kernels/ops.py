@@ -150,6 +150,8 @@ class CudaOps:
         self.fuse_recurrent_step = True
         #: the delta rule takes runs of several tokens in chunks of 32 (else token by token, as a decode step does)
         self.delta_in_chunks = True
+        #: rows from which a scored router's sums are a tensor-core product (where that product gives the same sums)
+        self.router_tc_from = 1
         #: so does gated linear attention
         self.gla_in_chunks = True
         #: a decode step's delta rule (convolution to gate) is one kernel while rows x heads fit the SMs
@@ -862,6 +864,11 @@ class CudaOps:
         if x.shape[1] != H * K:
             raise KernelError(f"per_head_linear: rows of {x.shape[1]} values are not {H} heads of {K}")
         out = torch.empty((T, H * N), dtype=self.dtype, device=self.device)
+        if T <= 16:
+            # a decode step: a warp per output and head instead of a few tiles
+            self.lib.call("rb_per_head_few_rows", _ptr(out), out.stride(0), self.code, _ptr(x), x.stride(0), _ptr(weight.w),
+                          self.code, T, H, N, K, self._stream())
+            return out
         self.lib.call("rb_gemm_simple_batched", _ptr(out), out.stride(0), self.code, _ptr(x), x.stride(0), _ptr(weight.w), K,
                       self.code, T, N, K, 0, 1.0, H, N, K, N * K, self._stream())
         return out
@@ -888,8 +895,9 @@ class CudaOps:
         ids = torch.empty((T, top), dtype=torch.int32, device=self.device)
         weights = torch.empty((T, top), dtype=torch.float32, device=self.device)
         extra = torch.empty((T, extra_rows), dtype=torch.float32, device=self.device) if extra_rows else None
-        if T >= 64 and router_tc is not None and self._tensor_core_ok(h, router_tc.w):
-            # many tokens: the sums (outputs and extra rows) on the tensor cores, then the choice
+        if T >= self.router_tc_from and router_tc is not None and self._tensor_core_ok(h, router_tc.w):
+            # the sums (outputs and extra rows) on the tensor cores, then the choice: also for a decode step, where the
+            # kernel that does both has a block per token (20 us at 8 tokens against 7 for the two)
             z = self.linear(h, router_tc, out_dtype=torch.float32)
             self.lib.call("rb_route_select_scored", _ptr(ids), _ptr(weights), _ptr(z), _ptr(correction), T, n, int(top),
                           int(groups), int(keep), {"softmax": 0, "sigmoid": 1}[scoring], int(extra_rows), _ptr(extra),

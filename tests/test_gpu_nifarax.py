@@ -327,10 +327,27 @@ def test_router_with_sigmoid_scores(n, top, T, K, extra):
         assert gate is None
 
 
-@pytest.mark.parametrize("n,top,T,K,extra", [(16, 4, 200, 64, 1), (5, 1, 64, 128, 0), (33, 8, 700, 256, 1), (6, 2, 63, 64, 1)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,N,K", [(1, 3, 8, 16), (8, 16, 128, 128), (16, 2, 33, 100), (17, 2, 33, 100), (5, 4, 7, 300), (300, 3, 40, 24)])
+def test_a_matrix_per_head(dtype, T, H, N, K):
+    """Few rows (a warp per output) and many (tiles) through the product with one matrix per head."""
+    ops = _ops(dtype)
+    g = torch.Generator().manual_seed(T * 10 + H)
+    x = torch.randn(T, H * K, generator=g).to(torch.bfloat16).double()
+    w = (torch.randn(H, N, K, generator=g) * 0.3).to(torch.bfloat16).double()
+    weight = ops.prepare_per_head(w.float().cuda())
+    got = ops.per_head_linear(x.to(dtype).cuda(), weight).float().cpu()
+    want = torch.einsum("thk,hnk->thn", x.view(T, H, K), w).reshape(T, H * N)
+    assert rel_err(got, want) <= (1e-5 if dtype == torch.float32 else 1e-2)
+    ops.check_errors()
+
+
+@pytest.mark.parametrize("n,top,T,K,extra", [(16, 4, 200, 64, 1), (5, 1, 64, 128, 0), (33, 8, 700, 256, 1), (6, 2, 63, 64, 1),
+                                             (32, 4, 8, 256, 1), (7, 3, 1, 64, 0)])
 def test_router_sums_on_the_tensor_cores(n, top, T, K, extra):
     """In bfloat16 mode a router whose float32 values are bfloat16 values has its sums (outputs and extra rows) made by
-    the tensor-core product from 64 tokens on; the choice and the weights are those of the plain sums."""
+    the tensor-core product, for a decode step's few rows as for a prompt's many; the choice and the weights are those
+    of the plain sums."""
     ops = _ops(torch.bfloat16)
     g = torch.Generator().manual_seed(n * 7 + top)
     h = torch.randn(T, K, generator=g).to(torch.bfloat16).double()
