@@ -194,6 +194,82 @@ __global__ void __launch_bounds__(256) input_filter_vec_kernel(T* __restrict__ o
   }
 }
 
+// ---------------------------------------------------------------- a decode step's rows between two sublayers
+// For rows that are each their own run: the gated result of the sublayer before (x += y * sigmoid(g + b); y null: none),
+// the norm in groups of the new x (h), and the filter on h from the ring (hf), whose row at the token's position
+// becomes h.  A block of eight warps per row and part of the row.
+template <typename TO>
+__global__ void __launch_bounds__(256) norm_filter_rows_kernel(TO* __restrict__ h, TO* __restrict__ hf, float* __restrict__ x,
+                                                               const float* __restrict__ y, const float* __restrict__ g,
+                                                               int64_t ldg, const float* __restrict__ bias,
+                                                               const float* __restrict__ w, int E, int groups, float eps,
+                                                               const float* __restrict__ taps, float* __restrict__ ring,
+                                                               const int* __restrict__ tok_slot,
+                                                               const int* __restrict__ tok_pos, int K) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int t = blockIdx.x, per = E / groups;
+  const int slot = tok_slot[t], pos = tok_pos[t];
+  float* row = x + (int64_t)t * E;
+  // blockIdx.y takes the row's parts in turn; all of the block's warps share a part
+  __shared__ float s_parts[8];                     // the warps' sums of squares
+  const int share = nw;
+  const int per4 = per >> 2;                         // 16 bytes a load: a lane takes four neighbouring channels at a time
+  for (int part = blockIdx.y; part < groups; part += gridDim.y) {
+    const int sub = warp;
+    const int c0 = part * per;
+    float ss = 0.f;
+    for (int i4 = sub * 32 + lane; i4 < per4; i4 += share * 32) {
+      const int c = c0 + 4 * i4;
+      float4 v = *reinterpret_cast<const float4*>(row + c);
+      if (y != nullptr) {
+        const float4 yy = *reinterpret_cast<const float4*>(y + (int64_t)t * E + c);
+        float4 z = *reinterpret_cast<const float4*>(g + (int64_t)t * ldg + c);
+        if (bias != nullptr) {
+          const float4 bb = *reinterpret_cast<const float4*>(bias + c);
+          z.x += bb.x; z.y += bb.y; z.z += bb.z; z.w += bb.w;
+        }
+        v.x = fmaf(yy.x, sigmoid_(z.x), v.x);
+        v.y = fmaf(yy.y, sigmoid_(z.y), v.y);
+        v.z = fmaf(yy.z, sigmoid_(z.z), v.z);
+        v.w = fmaf(yy.w, sigmoid_(z.w), v.w);
+        *reinterpret_cast<float4*>(row + c) = v;
+      }
+      ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+    ss = rb_warp_sum(ss);
+    __syncthreads();                               // (the sums of the part before have been read)
+    if (lane == 0) s_parts[warp] = ss;
+    __syncthreads();
+    ss = 0.f;
+    for (int k = 0; k < share; ++k) ss += s_parts[k];
+    const float r = 1.0f / sqrtf(ss / (float)per + eps);
+    for (int i4 = sub * 32 + lane; i4 < per4; i4 += share * 32) {
+      const int c = c0 + 4 * i4;
+      const float4 v = *reinterpret_cast<const float4*>(row + c);          // (the lane reads what it wrote itself)
+      const float4 ww = *reinterpret_cast<const float4*>(w + c);
+      float own[4] = {v.x * r * ww.x, v.y * r * ww.y, v.z * r * ww.z, v.w * r * ww.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) own[q] = rb_to_float<TO>(rb_from_float<TO>(own[q]));    // as the rows leave
+      store4(h + (int64_t)t * E + c, own[0], own[1], own[2], own[3]);
+      float acc[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[q] = fmaf(taps[(int64_t)(c + q) * K + (K - 1)], own[q], own[q]);
+      for (int d = 1; d < K; ++d) {
+        if (pos - d < 0) break;
+        const float4 rr = *reinterpret_cast<const float4*>(ring + ((int64_t)slot * K + (pos - d) % K) * E + c);
+        acc[0] = fmaf(taps[(int64_t)(c + 0) * K + (K - 1 - d)], rr.x, acc[0]);
+        acc[1] = fmaf(taps[(int64_t)(c + 1) * K + (K - 1 - d)], rr.y, acc[1]);
+        acc[2] = fmaf(taps[(int64_t)(c + 2) * K + (K - 1 - d)], rr.z, acc[2]);
+        acc[3] = fmaf(taps[(int64_t)(c + 3) * K + (K - 1 - d)], rr.w, acc[3]);
+      }
+      store4(hf + (int64_t)t * E + c, acc[0], acc[1], acc[2], acc[3]);
+      if (K > 1) *reinterpret_cast<float4*>(ring + ((int64_t)slot * K + pos % K) * E + c) = make_float4(own[0], own[1], own[2], own[3]);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- gated residual
 template <typename TG>
 __global__ void gated_add_kernel(float* __restrict__ x, const float* __restrict__ y, const TG* __restrict__ g, int64_t ldg,
@@ -287,6 +363,36 @@ RB_EXPORT int rb_input_filter(void* out, const void* h, int dtype, const float* 
   else
     RB_FAIL("rb_input_filter: unknown dtype %d", dtype);
   RB_CHECK_LAUNCH("rb_input_filter");
+  return 0;
+}
+
+// Whether these sizes take rb_norm_filter_rows: parts of the row and the gate's rows in multiples of four values.
+RB_EXPORT int rb_norm_filter_rows_supports(int E, int groups, long long ldg) {
+  return groups >= 1 && E > 0 && E % groups == 0 && (E / groups) % 4 == 0 && ldg % 4 == 0;
+}
+
+// Rows that are each their own run (a decode step): x += y * sigmoid(g + bias) (y null: nothing is added), then
+// h = norm in groups of x, hf = h filtered from the ring [n_slots, K, E], which takes h at the row's position.
+RB_EXPORT int rb_norm_filter_rows(void* h, void* hf, int dtype, float* x, const float* y, const float* g, int64_t ldg,
+                                  const float* bias, const float* w, int T, int E, int groups, float eps, const float* taps,
+                                  float* ring, const int* tok_slot, const int* tok_pos, int K, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(groups >= 1 && E > 0 && E % groups == 0 && K >= 1 && (K == 1 || ring != nullptr),
+             "rb_norm_filter_rows: bad sizes E=%d groups=%d K=%d", E, groups, K);
+  RB_REQUIRE(rb_norm_filter_rows_supports(E, groups, ldg) && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0 &&
+                 (uintptr_t)g % 16 == 0 && (uintptr_t)bias % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)ring % 16 == 0 &&
+                 (uintptr_t)h % 16 == 0 && (uintptr_t)hf % 16 == 0,
+             "rb_norm_filter_rows: parts of %d values or addresses do not allow 16 bytes a load", E / groups);
+  const int threads = 256;
+  const size_t smem = 0;
+  const dim3 grid(T, groups < 64 ? groups : 64);
+  if (dtype == RB_F32)
+    RB_LAUNCH("norm_filter_rows_kernel", (norm_filter_rows_kernel<float>), grid, threads, smem, stream, (float*)h, (float*)hf, x, y, g, ldg, bias, w, E, groups, eps, taps, ring, tok_slot, tok_pos, K);
+  else if (dtype == RB_BF16)
+    RB_LAUNCH("norm_filter_rows_kernel", (norm_filter_rows_kernel<__nv_bfloat16>), grid, threads, smem, stream, (__nv_bfloat16*)h, (__nv_bfloat16*)hf, x, y, g, ldg, bias, w, E, groups, eps, taps, ring, tok_slot, tok_pos, K);
+  else
+    RB_FAIL("rb_norm_filter_rows: unknown dtype %d", dtype);
+  RB_CHECK_LAUNCH("rb_norm_filter_rows");
   return 0;
 }
 

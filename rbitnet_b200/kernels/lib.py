@@ -61,6 +61,8 @@ _SIGNATURES = {
     "rb_rmsnorm_grouped": [P, I, P, P, I, I, I, F, P],
     "rb_input_filter": [P, P, I, P, P, P, P, P, I, I, I, P],
     "rb_gated_add": [P, P, P, L, I, P, I, I, P],
+    "rb_norm_filter_rows_supports": [I, I, L],
+    "rb_norm_filter_rows": [P, P, I, P, P, P, L, P, P, I, I, I, F, P, P, P, P, I, P],
     "rb_add_scaled_rows": [P, P, P, L, I, I, P],
     "rb_softcap": [P, ctypes.c_longlong, F, P],
     "rb_gla_decay": [P, P, L, I, P, P, I, I, I, F, I, P],

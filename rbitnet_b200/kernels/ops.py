@@ -150,6 +150,8 @@ class CudaOps:
         self.fuse_recurrent_step = True
         #: the delta rule takes runs of several tokens in chunks of 32 (else token by token, as a decode step does)
         self.delta_in_chunks = True
+        #: a decode step's gated addition, norm in groups and filter between two sublayers are one kernel
+        self.fuse_norm_filter = True
         #: rows from which a scored router's sums are a tensor-core product (where that product gives the same sums)
         self.router_tc_from = 1
         #: so does gated linear attention
@@ -779,6 +781,29 @@ class CudaOps:
             self.lib.call("rb_conv_tail_update", _ptr(ring), _ptr(h), h.stride(0), 0, self.code, c_void_p(0), _ptr(first),
                           _ptr(count), _ptr(meta.tok_slot), _ptr(meta.tok_pos), n_runs, C, K, self._stream())
         return out
+
+    def norm_filter_rows(self, x: torch.Tensor, w: torch.Tensor, groups: int, eps: float, taps: torch.Tensor,
+                         ring: Optional[torch.Tensor], meta, add=None):
+        """For a step of one token per sequence, in one launch: ``add`` = (y, logits, bias): x += y * sigmoid(logits +
+        bias) first; then (h, hf): the norm in groups of x and its filtered rows (``rmsnorm_grouped`` and
+        ``input_filter``), the ring moved on.  None where this step or these sizes do not take it."""
+        if not (self.fuse_norm_filter and meta.single_token):
+            return None
+        self._check(x, torch.float32, "norm_filter_rows rows")
+        T, E = x.shape
+        y = g = b = None
+        if add is not None:
+            y, g, b = add
+            if g.dtype != torch.float32 or y.dtype != torch.float32:
+                return None
+        if not self.lib.raw("rb_norm_filter_rows_supports")(E, int(groups), g.stride(0) if g is not None else 0):
+            return None
+        h = torch.empty((T, E), dtype=self.dtype, device=self.device)
+        hf = torch.empty((T, E), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_norm_filter_rows", _ptr(h), _ptr(hf), self.code, _ptr(x), _ptr(y), _ptr(g),
+                      g.stride(0) if g is not None else 0, _ptr(b), _ptr(w), T, E, int(groups), float(eps), _ptr(taps),
+                      _ptr(ring), _ptr(meta.tok_slot), _ptr(meta.tok_pos), taps.shape[1], self._stream())
+        return h, hf
 
     def gated_add(self, x: torch.Tensor, y: torch.Tensor, logits: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
         """x += y * sigmoid(logits + bias), value by value, in float32."""

@@ -178,15 +178,44 @@ class GatedPreNormBlock:
         return self._parts
 
     def run(self, ctx, x, entry: int):
+        # Where the operations have it, a step of one token per sequence takes what lies between two sublayers (the
+        # gated result of the one, the norm and the filter of the next) as one operation; a gated result therefore
+        # waits until the next norm, or the block's end, asks for the residual stream.
+        rows_between = getattr(ctx.ops, "norm_filter_rows", None)
+        waiting = None                                     # (gate, y, logits) not yet added to x
+
+        def settle():
+            nonlocal waiting
+            if waiting is not None:
+                waiting[0].apply(ctx, x, waiting[1], waiting[2])
+                waiting = None
+
         for part, norm, filter_name, filt, gate, is_mixer in self.sublayers:
-            h = norm.forward(ctx, x)
+            h = hf = None
+            groups = getattr(norm, "groups", None)
+            if rows_between is not None and filt is not None and groups is not None and hasattr(filt, "w"):
+                add = None
+                if waiting is not None:
+                    addend = getattr(waiting[0], "addend", None)
+                    if addend is None:
+                        settle()
+                    else:
+                        add = addend(waiting[1], waiting[2])
+                got = rows_between(x, norm.weight, groups, norm.eps, filt.w, ctx.part_state(entry, filter_name), ctx.meta,
+                                   add=add)
+                if got is not None:
+                    h, hf = got
+                    waiting = None
+            if h is None:
+                settle()
+                h = norm.forward(ctx, x)
+                hf = filt.forward(ctx, h, ctx.part_state(entry, filter_name)) if filt is not None else h
             logits = gate.logits(ctx, h) if gate is not None else None
-            if filt is not None:
-                h = filt.forward(ctx, h, ctx.part_state(entry, filter_name))
             into = x if gate is None else None
-            y = part.forward(ctx, h, entry, accumulate_into=into) if is_mixer else part.forward(ctx, h, accumulate_into=into)
+            y = part.forward(ctx, hf, entry, accumulate_into=into) if is_mixer else part.forward(ctx, hf, accumulate_into=into)
             if gate is not None:
-                gate.apply(ctx, x, y, logits)
+                waiting = (gate, y, logits)
+        settle()
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -58,6 +58,10 @@ class SigmoidGate(ResultGate):
     def apply(self, ctx, x, y, logits):
         ctx.ops.gated_add(x, y, logits, self.b)
 
+    def addend(self, y, logits):
+        """(y, logits, bias): what ``apply`` would add, for an operation that adds it together with what follows."""
+        return y, logits, self.b
+
 
 register_part("input_filter", "causal_taps", CausalTapsFilter)
 register_part("result_gate", "sigmoid_linear", SigmoidGate)

@@ -183,6 +183,46 @@ def test_input_filter(dtype, C, K, T):
     ops.check_errors()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("E,groups,K,with_add", [(64, 2, 3, True), (100, 5, 4, False), (96, 1, 1, True), (2048, 2, 4, True),
+                                                 (72, 9, 6, True), (70, 5, 3, True)])
+def test_rows_between_two_sublayers_in_one_kernel(dtype, E, groups, K, with_add):
+    """A decode step's gated addition, norm in groups and filter as one kernel against the three kernels: the same
+    residual stream, and normed rows, filtered rows and ring that agree to rounding, at positions before and after the ring is full and in a slot
+    whose ring holds stale rows."""
+    ops = _ops(dtype)
+    g = torch.Generator().manual_seed(E + K)
+    T = 5
+    w = torch.randn(E, generator=g).cuda()
+    taps = torch.randn(E, K, generator=g).cuda()
+    bias = torch.randn(E, generator=g).cuda()
+    ring_a = torch.randn(8, K, E, generator=g).cuda() if K > 1 else None
+    ring_b = ring_a.clone() if K > 1 else None
+    x_a = torch.randn(T, E, generator=g).cuda()
+    x_b = x_a.clone()
+    from rbitnet_b200.engine.step import SeqChunk, build_meta
+    for pos in (0, 1, 2, 7, 100):
+        meta = build_meta([SeqChunk(slot, pos, 1, i) for i, slot in enumerate((3, 0, 5, 1, 6))], np.zeros(T, dtype=np.int32),
+                          np.zeros(0, dtype=np.int32), ops.device)
+        y = torch.randn(T, E, generator=g).cuda()
+        z = torch.randn(T, E, generator=g).cuda()
+        ops.fuse_norm_filter = True
+        got = ops.norm_filter_rows(x_a, w, groups, 1e-5, taps, ring_a, meta, add=(y, z, bias) if with_add else None)
+        if (E // groups) % 4:
+            assert got is None                       # parts that do not allow 16 bytes a load: the three kernels
+            return
+        assert got is not None
+        if with_add:
+            ops.gated_add(x_b, y, z, bias)
+        h = ops.rmsnorm_grouped(x_b, w, groups, 1e-5)
+        hf = ops.input_filter(h, taps, ring_b, meta)
+        tol = 1e-6 if dtype == torch.float32 else 1e-2        # (the norm alone adds its squares up in another order)
+        assert torch.equal(x_a, x_b)
+        assert rel_err(got[0].float().cpu(), h.double().cpu()) <= tol and rel_err(got[1].float().cpu(), hf.double().cpu()) <= tol
+        assert K == 1 or rel_err(ring_a.cpu(), ring_b.double().cpu()) <= tol
+    ops.check_errors()
+
+
 def test_gated_add_and_softcap():
     ops = _ops(torch.float32)
     g = torch.Generator().manual_seed(3)
