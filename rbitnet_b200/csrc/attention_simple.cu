@@ -74,12 +74,13 @@ int launch(T* out, const T* q, RbPagedLayer c, const int* tok_pos, const int* to
            float scale, int window, cudaStream_t stream) {
   const int64_t warps = (int64_t)n_tokens * H;
   const int blocks = (int)((warps + 3) / 4);
-  const int epl = (c.head_dim + 31) / 32;
+  int epl = (c.head_dim + 31) / 32;
+  if (epl > 8) epl = epl <= 12 ? 12 : (epl <= 16 ? 16 : (epl <= 24 ? 24 : (epl <= 32 ? 32 : epl)));   // head sizes up to 1,024
 #define CASE(E) \
   case E: RB_LAUNCH("attn_simple_kernel", (attn_simple_kernel<T, E>), blocks, 128, 0, stream, out, q, c, tok_pos, tok_slot, n_tokens, H, scale, window); break;
   switch (epl) {
-    CASE(1) CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8)
-    default: RB_FAIL("rb_attention_simple: head_dim %d exceeds 256", c.head_dim);
+    CASE(1) CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8) CASE(12) CASE(16) CASE(24) CASE(32)
+    default: RB_FAIL("rb_attention_simple: head_dim %d exceeds 1024", c.head_dim);
   }
 #undef CASE
   RB_CHECK_LAUNCH("rb_attention_simple");
@@ -94,7 +95,7 @@ RB_EXPORT int rb_attention_simple(void* out, const void* q, int dtype, const voi
                                   int window, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   RB_REQUIRE(H > 0 && Kh > 0 && H % Kh == 0, "rb_attention_simple: heads %d not a multiple of kv heads %d", H, Kh);
-  RB_REQUIRE(D > 0 && D <= 256, "rb_attention_simple: head_dim %d must be in 1..256", D);
+  RB_REQUIRE(D > 0 && D <= 1024, "rb_attention_simple: head_dim %d must be in 1..1024", D);
   RbPagedLayer c{(void*)cache_k, (void*)cache_v, page_table, max_pages, page_size, Kh, D};
   if (dtype == RB_F32)
     return launch<float>((float*)out, (const float*)q, c, tok_pos, tok_slot, n_tokens, H, scale, window, stream);

@@ -314,20 +314,21 @@ def test_the_memory_keeps_a_far_token():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,D,Dv,Rq,R", [(4, 16, 8, 24, 32), (2, 24, 40, 16, 16), (3, 24, 24, 20, 40), (4, 32, 64, 96, 64),
-                                         (16, 16, 32, 64, 128), (1, 8, 8, 8, 200), (2, 64, 16, 7, 9)])
+                                         (16, 16, 32, 64, 128), (1, 8, 8, 8, 200), (2, 64, 16, 7, 9), (2, 16, 16, 24, 320)])
 def test_latent_attention_part(dtype, H, D, Dv, Rq, R):
     """Attention through latents over the paged cache: whole, in portions across a page border, and token by token;
-    latents of sizes that the tensor-core attention kernels take and refuse."""
+    latents of sizes that the tensor-core attention kernels take and refuse, and one wider than any of them takes."""
     from rbitnet_b200.cache import SequenceCache
     from rbitnet_b200.parts.latent import LatentAttention
     ops = _ops(dtype)
     g = torch.Generator().manual_seed(H * 100 + D)
     E, T = 64, 90
-    part = LatentAttention(E, H, D, Dv, Rq, R, scale=0.35, norm_eps=1e-5)
+    scale = 0.35 if R <= 256 else 0.12        # (a wide latent's sums are large: scores that bfloat16 still resolves)
+    part = LatentAttention(E, H, D, Dv, Rq, R, scale=scale, norm_eps=1e-5)
     w = _random_weights(part, g, 0.4)
     part.bind({k: v.float().cuda() for k, v in w.items()}, ops)
     h = torch.randn(T, E, generator=g).to(torch.bfloat16).double()
-    m = {"heads": H, "dim": D, "vdim": Dv, "scale": 0.35}
+    m = {"heads": H, "dim": D, "vdim": Dv, "scale": scale}
     want = plain.latent_attention(h, m, w, 1e-5)
     for cuts in ([0, T], [0, 60, 64, 65, T], [0, 50] + list(range(51, T + 1))):
         cache = SequenceCache({0: part.cache_need()}, {}, {}, 64 * 4, 1024, dtype, ops.device)
