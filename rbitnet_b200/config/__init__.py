@@ -3,9 +3,10 @@ from .llama import LlamaConfig
 from .safuvik import SafuvikConfig
 from .vaderax import VaderaxConfig
 from .nifarax import NifaraxConfig
+from .gozotar import GozotarConfig
 from .registry import (register_architecture, unregister_architecture, known_architectures,
                        get_architecture, architecture_of, config_from_dict, load_config)
 
-__all__ = ["ModelConfig", "ConfigError", "read_config_json", "LlamaConfig", "SafuvikConfig", "VaderaxConfig", "NifaraxConfig",
+__all__ = ["ModelConfig", "ConfigError", "read_config_json", "LlamaConfig", "SafuvikConfig", "VaderaxConfig", "NifaraxConfig", "GozotarConfig",
            "register_architecture", "unregister_architecture", "known_architectures",
            "get_architecture", "architecture_of", "config_from_dict", "load_config"]

@@ -15,6 +15,10 @@ from ..parts import ModelSpec, build_block, build_part
 from ..weights import check_tensors
 
 
+#: the key of the state area that holds every sequence's last token (for an embedding of token pairs)
+PREVIOUS_TOKEN = ("model", "previous_token")
+
+
 class Model:
     def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], ops):
         for n in check_tensors(spec.expected_shapes(), tensors, ignorable=spec.ignorable):
@@ -44,6 +48,11 @@ class Model:
             self.embedding_norm.bind({k: tensors[n].to(dev) for k, n in spec.embedding_norm_names.items()}, ops)
         self.logit_softcap = float(getattr(spec, "logit_softcap", 0.0) or 0.0)
         self.embedding = ops.prepare_embedding(tensors[spec.embedding_name])
+        self.embedding_pairs = self.pair_hash = None
+        pairs = getattr(spec, "embedding_pairs", None)
+        if pairs is not None:
+            self.embedding_pairs = ops.prepare_embedding(tensors[pairs["name"]])
+            self.pair_hash = (int(pairs["buckets"]), int(pairs["mul_prev"]), int(pairs["mul_cur"]))
         if spec.head_name is None:
             self.head = ops.prepare_linear([self.embedding])     # tied: the table itself
         else:
@@ -95,6 +104,9 @@ class Model:
                 st = need() if need is not None else None
                 if st:
                     state_needs[("part", e, name)] = st
+        if self.embedding_pairs is not None:
+            from ..parts.base import StateNeed
+            state_needs[PREVIOUS_TOKEN] = StateNeed((1,), torch.int32)
         return cache_needs, reads, state_needs
 
     def weight_bytes(self) -> int:
@@ -133,7 +145,12 @@ class Model:
     def forward(self, ctx) -> Optional[torch.Tensor]:
         """Runs the step's tokens; returns float32 logits [wanted rows, vocab] or None."""
         ops, meta = ctx.ops, ctx.meta
-        x = ops.embed(meta.token_ids, self.embedding, self.embedding_scale)   # float32 residual stream [T, E]
+        if self.embedding_pairs is None:
+            x = ops.embed(meta.token_ids, self.embedding, self.embedding_scale)   # float32 residual stream [T, E]
+        else:
+            # plus a row chosen by the pair (previous token, token); the previous token belongs to the sequence
+            x = ops.embed_pairs(meta, self.embedding, self.embedding_scale, self.embedding_pairs, self.pair_hash,
+                                ctx.cache.state(PREVIOUS_TOKEN))
         if self.embedding_norm is not None:
             x = self.embedding_norm.forward(ctx, x, out_dtype=torch.float32)
         s = self.residual_streams
@@ -156,6 +173,15 @@ class Model:
                 pending = block.run(ctx, x, e, pending=pending, next_read=next_read)
                 if taps is not None:
                     taps.append(ops.streams_sum(x, s) if s > 1 else x.clone())
+                continue
+            if getattr(block, "chains_rows", False):
+                # a block whose last addition also leaves the rows in the compute dtype, which the block after reads
+                # (see parts/block.py); the last block of the schedule leaves none
+                after = self.blocks[schedule[e + 1].layer] if e + 1 < len(schedule) else None
+                hand_on = getattr(after, "chains_rows", False) and not schedule[e + 1].adds_embedding
+                pending = block.run(ctx, x, e, rows=pending, want_rows=hand_on)
+                if taps is not None:
+                    taps.append(x.clone())
                 continue
             if not getattr(block, "chains_norms", False):
                 block.run(ctx, x, e)

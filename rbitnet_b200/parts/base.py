@@ -19,6 +19,8 @@ Roles:
                     fixed-size state per sequence (``state_need``), which the block hands to it
   result_gate       logits(ctx, h) from the sublayer's unfiltered input, and apply(ctx, x, y, logits): how the
                     sublayer's result y enters the residual stream x
+  token_input       forward(ctx, x, h): adds to the residual stream x something made from the rows' token ids
+                    (``ctx.meta.token_ids``) and from h, the same rows in the compute dtype
 """
 from __future__ import annotations
 
@@ -130,6 +132,16 @@ class ResultGate(Part):
 
     def apply(self, ctx, x: torch.Tensor, y: torch.Tensor, logits) -> None:
         """x (float32 [T, E], the residual stream) takes y (float32 [T, E]) in."""
+        raise NotImplementedError
+
+
+class TokenInput(Part):
+    """Adds to the residual stream a function of each row's token id and of the row itself."""
+    role = "token_input"
+
+    def forward(self, ctx, x: torch.Tensor, h: torch.Tensor, want_rounded: bool = False):
+        """x: float32 [T, E], changed in place; h: the same rows in the compute dtype.  With ``want_rounded`` the new
+        rows are returned in the compute dtype as well."""
         raise NotImplementedError
 
 

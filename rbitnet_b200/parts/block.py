@@ -218,6 +218,54 @@ class GatedPreNormBlock:
         settle()
 
 
+class PostNormBlock:
+    """Sublayers that read the residual stream itself and whose RESULTS are normed:
+
+        x <- x + norm1(mixer(x));   x <- x + norm2(feed_forward(x));   x <- x + token_input(x, token)
+
+    Parts: "mixer" with "mixer_norm"; optionally "feed_forward" with "ffn_norm"; optionally "token_input" (role
+    "token_input").  The norms are asked through ``add_to`` (an RMS norm with its weight, layer scale included, as one
+    vector).  What a sublayer reads is x rounded to the compute dtype; the kernel that adds a normed result also
+    leaves those rows for the next sublayer, so a layer has no kernel that only rounds, but for the very first
+    sublayer of a step: the last addition of a block hands its rows to the block after it (``chains_rows``)."""
+
+    chains_rows = True
+
+    def __init__(self, spec):
+        self.spec = spec
+        self._parts = build_parts(spec)
+        missing = [n for n in ("mixer", "mixer_norm") if n not in self._parts]
+        if missing:
+            raise ValueError(f"a post_norm block needs the parts {missing}")
+        if ("feed_forward" in self._parts) != ("ffn_norm" in self._parts):
+            raise ValueError("a post_norm block has a feed-forward with its norm, or neither")
+        p = self._parts
+        self.mixer, self.mixer_norm = p["mixer"], p["mixer_norm"]
+        self.feed_forward, self.ffn_norm = p.get("feed_forward"), p.get("ffn_norm")
+        self.token_input = p.get("token_input")
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and not hasattr(norm, "add_to"):
+                raise ValueError("a post_norm block needs norms that can be added to the residual stream (add_to)")
+
+    def parts(self):
+        return self._parts
+
+    def run(self, ctx, x, entry: int, rows=None, want_rows: bool = True):
+        """``rows``: x in the compute dtype, if the block before left it.  Returns the same for the block after
+        (None if ``want_rows`` is false: nobody reads them)."""
+        h = rows if rows is not None else ctx.ops.round_rows(x)
+        last = "token_input" if self.token_input is not None else ("ffn" if self.feed_forward is not None else "mixer")
+        y = self.mixer.forward(ctx, h, entry, accumulate_into=None)
+        h = self.mixer_norm.add_to(ctx, x, y, want_rounded=want_rows or last != "mixer")
+        if self.feed_forward is not None:
+            y = self.feed_forward.forward(ctx, h, accumulate_into=None)
+            h = self.ffn_norm.add_to(ctx, x, y, want_rounded=want_rows or last != "ffn")
+        if self.token_input is not None:
+            h = self.token_input.forward(ctx, x, h, want_rounded=want_rows)
+        return h if want_rows else None
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "post_norm", PostNormBlock)
 register_part("block", "pre_norm_gated", GatedPreNormBlock)
 register_part("block", "multi_stream", StreamBlock)

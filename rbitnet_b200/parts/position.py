@@ -14,6 +14,10 @@ lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), rot_dim - 1) and
 ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns with
 f_i * (ramp_i / factor + 1 - ramp_i), and sines and cosines are multiplied by
 0.1 ln(factor) + 1.
+``scaling`` with "kind": "wavelength" (keys factor, low, high, original) decides pair by pair from the pair's
+wavelength l = 2 pi / f:  f stays where l < original / high; it becomes f / factor where l > original / low; between
+the two, with s = (original / l - low) / (high - low), it becomes (1 - s) f / factor + s f.  Sines and cosines keep
+magnitude 1.
 """
 from __future__ import annotations
 
@@ -37,7 +41,9 @@ class RotaryEncoding(PositionEncoding):
         self.max_positions = int(max_positions)
         self.scaling = dict(scaling) if scaling else None
         if self.scaling:
-            missing = [k for k in ("factor", "original", "fast", "slow") if k not in self.scaling]
+            by_wavelength = self.scaling.get("kind") == "wavelength"
+            missing = [k for k in (("factor", "original", "low", "high") if by_wavelength else
+                                   ("factor", "original", "fast", "slow")) if k not in self.scaling]
             if missing:
                 raise ValueError(f"rotary scaling needs {', '.join(missing)}")
         self.inv_freq = self.freq64 = None
@@ -52,6 +58,13 @@ class RotaryEncoding(PositionEncoding):
             return f, 1.0
         sc = self.scaling
         factor, original = float(sc["factor"]), float(sc["original"])
+        if sc.get("kind") == "wavelength":
+            low, high = float(sc["low"]), float(sc["high"])
+            length = 2.0 * math.pi / f
+            s = ((original / length - low) / (high - low)).clamp(0.0, 1.0) if high != low else torch.ones_like(f)
+            blended = (1.0 - s) * f / factor + s * f
+            out = torch.where(length < original / high, f, torch.where(length > original / low, f / factor, blended))
+            return out, 1.0
 
         def pair_of(turns):
             return n * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))

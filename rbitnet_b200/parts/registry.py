@@ -4,7 +4,8 @@ from __future__ import annotations
 
 from typing import Callable, Dict
 
-ROLES = ("mixer", "feed_forward", "norm", "position", "block", "connection", "input_filter", "result_gate")
+ROLES = ("mixer", "feed_forward", "norm", "position", "block", "connection", "input_filter", "result_gate",
+         "token_input")
 _PARTS: Dict[str, Dict[str, Callable]] = {r: {} for r in ROLES}
 _ALIASES = {"mixer_norm": "norm", "ffn_norm": "norm"}
 

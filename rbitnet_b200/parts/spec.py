@@ -108,6 +108,11 @@ class ModelSpec:
     #: the logits are capped softly: cap * tanh(logits / cap) (0.0: as they are)
     logit_softcap: float = 0.0
 
+    #: a second embedding added to the first: the row (previous token * mul_prev + token * mul_cur) mod buckets of the
+    #: table "name" ([buckets + 1, width]); a sequence's first token takes the last row.  Keys: name, buckets,
+    #: mul_prev, mul_cur
+    embedding_pairs: Optional[dict] = None
+
     def tensor_table(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         """name -> (shape, init kind) of every tensor the model needs."""
         from .registry import build_part
@@ -126,6 +131,8 @@ class ModelSpec:
         if self.embedding_norm is not None:
             for key, (shape, kind) in build_part("norm", self.embedding_norm).weight_shapes().items():
                 table[self.embedding_norm_names[key]] = (tuple(shape), kind)
+        if self.embedding_pairs is not None:
+            table[self.embedding_pairs["name"]] = ((int(self.embedding_pairs["buckets"]) + 1, self.width), "matrix")
         if self.head_name is not None:
             table[self.head_name] = ((self.vocab_size, self.width), "matrix")
         return table

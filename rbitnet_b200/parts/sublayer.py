@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import InputFilter, ResultGate, StateNeed
+from .base import InputFilter, ResultGate, TokenInput, StateNeed
 from .registry import register_part
 
 
@@ -65,3 +65,37 @@ class SigmoidGate(ResultGate):
 
 register_part("input_filter", "causal_taps", CausalTapsFilter)
 register_part("result_gate", "sigmoid_linear", SigmoidGate)
+
+
+class GatedTokenEmbedding(TokenInput):
+    """x += rms(P (gelu_tanh(G x) * e)) * w: e is the row's slice of a second embedding table ("embed": [vocab,
+    n_slices * dim], this part's slice is ``index``), G ("gate") is [dim, width], P ("proj") [width, dim], and the RMS
+    norm over the width has a plain weight w ("norm").  The table is kept as this part's own [vocab, dim] slice."""
+
+    def __init__(self, width: int, dim: int, vocab: int, index: int, n_slices: int, eps: float):
+        self.width, self.dim, self.vocab = int(width), int(dim), int(vocab)
+        self.index, self.n_slices, self.eps = int(index), int(n_slices), float(eps)
+        if not 0 <= self.index < self.n_slices or self.dim < 1:
+            raise ValueError("gated token embedding: the slice must lie inside the table")
+        self.table = self.w_gate = self.w_proj = self.norm_w = None
+
+    def weight_shapes(self):
+        return {"embed": ((self.vocab, self.n_slices * self.dim), "matrix"), "gate": ((self.dim, self.width), "matrix"),
+                "proj": ((self.width, self.dim), "matrix"), "norm": ((self.width,), "norm")}
+
+    def bind(self, weights, ops):
+        d = self.dim
+        self.table = ops.prepare_embedding(weights["embed"][:, self.index * d:(self.index + 1) * d])
+        self.w_gate = ops.prepare_linear([weights["gate"]])
+        self.w_proj = ops.prepare_linear([weights["proj"]])
+        self.norm_w = weights["norm"].to(device=ops.device, dtype=torch.float32).contiguous()
+
+    def forward(self, ctx, x, h, want_rounded=False):
+        ops = ctx.ops
+        a = ops.linear(h, self.w_gate, out_dtype=torch.float32)                 # [T, dim]
+        g = ops.token_gate(a, self.table, ctx.meta.token_ids)                   # gelu_tanh(a) * e, compute dtype
+        y = ops.linear(g, self.w_proj, out_dtype=torch.float32)                 # [T, width]
+        return ops.norm_add(x, y, self.norm_w, self.eps, want_rounded=want_rounded)
+
+
+register_part("token_input", "gated_embedding", GatedTokenEmbedding)

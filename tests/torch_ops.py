@@ -428,7 +428,7 @@ class TorchOps:
                 view.v[page, :, p % view.page_size, :] = v[t].to(view.v.dtype)
         return q.to(self.dtype)
 
-    def attention(self, q, meta, view, n_heads, scale, window):
+    def attention(self, q, meta, view, n_heads, scale, window, sinks=None, softcap=0.0):
         T, H, D = q.shape
         G = H // view.n_kv_heads
         out = torch.zeros(T, H * D, dtype=torch.float32)
@@ -441,9 +441,150 @@ class TorchOps:
             vs = view.v[pages, :, idx % view.page_size, :].to(torch.float32)
             for h in range(H):
                 s = (ks[:, h // G, :] @ q[t, h].to(torch.float32)) * scale
-                pr = torch.softmax(s, dim=0)
+                if softcap:
+                    s = softcap * torch.tanh(s / softcap)
+                if sinks is not None:
+                    pr = torch.softmax(torch.cat([s, sinks[h:h + 1].float()]), dim=0)[:-1]
+                else:
+                    pr = torch.softmax(s, dim=0)
                 out[t, h * D:(h + 1) * D] = pr @ vs[:, h // G, :]
         return out.to(self.dtype)
+
+    # ---- rows that sublayers read as they are, and results that are normed
+    def round_rows(self, x):
+        return x.to(self.dtype)
+
+    def norm_add(self, x, y, w, eps, want_rounded=False):
+        y = y.float()
+        x += y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * w
+        return x.to(self.dtype) if want_rounded else None
+
+    def token_gate(self, a, table, ids):
+        a = a.float()
+        g = 0.5 * a * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (a + 0.044715 * a ** 3)))
+        return (g * table[ids.long()].float()).to(self.dtype)
+
+    def embed_pairs(self, meta, table, scale, pair_table, pair_hash, previous):
+        buckets, mul_prev, mul_cur = pair_hash
+        ids = meta.token_ids.long()
+        x = table[ids].to(torch.float32) * scale
+        for first, n, slot in self._runs(meta):
+            for t in range(first, first + n):
+                if int(meta.tok_pos[t]) == 0:
+                    row = buckets
+                else:
+                    prev = int(ids[t - 1]) if t > first else int(previous[slot, 0])
+                    row = (prev * mul_prev + int(ids[t]) * mul_cur) % buckets
+                x[t] += pair_table[row].float()
+            previous[slot, 0] = int(ids[first + n - 1])
+        return x
+
+    def _turn(self, t_, table, pos):
+        """t_ [T, heads, D], changed in place: the first rot values of every head turned by position."""
+        freq, magnitude, interleaved, rot = table
+        ang = pos.to(torch.float64)[:, None] * freq[None, :]
+        c, s_ = (torch.cos(ang) * magnitude).float()[:, None, :], (torch.sin(ang) * magnitude).float()[:, None, :]
+        if interleaved:
+            a, b = t_[..., 0:rot:2].clone(), t_[..., 1:rot:2].clone()
+            t_[..., 0:rot:2], t_[..., 1:rot:2] = a * c - b * s_, b * c + a * s_
+        else:
+            a, b = t_[..., :rot // 2].clone(), t_[..., rot // 2:rot].clone()
+            t_[..., :rot // 2], t_[..., rot // 2:rot] = a * c - b * s_, b * c + a * s_
+
+    def qk_prepare(self, proj, meta, view, n_heads, head_dim, value_dim, table, norm, q_norm_w, k_norm_w, eps, conv=None,
+                   tail=None, values_are_keys=False, v_mix=None, gate_heads=False):
+        T, H, D, Dv, Kh, Dc = proj.shape[0], n_heads, head_dim, value_dim, view.n_kv_heads, view.head_dim
+        x = proj.float()
+        C = (H + Kh) * D
+        qk = x[:, :C].clone()
+        if conv is not None:
+            K = conv.shape[1]
+            for first, n, slot in self._runs(meta):
+                p0 = int(meta.tok_pos[first])
+                hist = torch.zeros(K - 1 + n, C)
+                for j in range(1, K):
+                    if p0 - j >= 0:
+                        hist[K - 1 - j] = tail[slot, (p0 - j) % K]
+                hist[K - 1:] = x[first:first + n, :C]
+                for i in range(n):
+                    qk[first + i] = (hist[i:i + K] * conv.T).sum(0)
+                for i in range(max(0, n - K), n):
+                    tail[slot, (p0 + i) % K] = x[first + i, :C]
+        q, k = qk[:, :H * D], qk[:, H * D:]
+        if values_are_keys:
+            v = k.reshape(T, Kh, D).clone()
+            at = C
+        else:
+            v = x[:, C:C + Kh * Dv].reshape(T, Kh, Dv)
+            at = C + Kh * Dv
+            if v_mix is not None:
+                lam, first_proj, first_at = v_mix
+                v = (1.0 - lam) * v + lam * first_proj.float()[:, first_at:first_at + Kh * Dv].reshape(T, Kh, Dv)
+        gates = x[:, at:at + H].to(self.dtype) if gate_heads else None
+        rms = lambda z: z / torch.sqrt((z * z).mean(-1, keepdim=True) + eps)
+        if norm == "projection":
+            q, k = rms(q) * q_norm_w, rms(k) * k_norm_w
+        q, k = q.reshape(T, H, D).clone(), k.reshape(T, Kh, D).clone()
+        if norm == "head_weight":
+            q, k = rms(q) * q_norm_w, rms(k) * k_norm_w
+        if table is not None:
+            self._turn(q, table, meta.tok_pos)
+            self._turn(k, table, meta.tok_pos)
+        qo = torch.zeros(T, H, Dc)
+        qo[..., :D] = q
+        for t in range(T):
+            p, slot = int(meta.tok_pos[t]), int(meta.tok_slot[t])
+            page = int(view.page_table[slot, p // view.page_size])
+            view.k[page, :, p % view.page_size, :] = 0
+            view.v[page, :, p % view.page_size, :] = 0
+            view.k[page, :, p % view.page_size, :D] = k[t].to(view.k.dtype)
+            view.v[page, :, p % view.page_size, :Dv] = v[t].to(view.v.dtype)
+        return qo.to(self.dtype), gates
+
+    def latent_rotate_append(self, down, n_heads, head_dim, rot_dim, kv_rank, table, w, eps, meta, view):
+        x = down.float()
+        T, H, D, R, C = x.shape[0], n_heads, head_dim, rot_dim, kv_rank
+        q = x[:, :H * (D + R)].reshape(T, H, D + R).clone()
+        c = x[:, H * (D + R):H * (D + R) + C]
+        c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * w
+        kr = x[:, H * (D + R) + C:H * (D + R) + C + R].reshape(T, 1, R).clone()
+        if R:
+            qr = q[..., D:].clone()
+            self._turn(qr, table, meta.tok_pos)
+            q[..., D:] = qr
+            self._turn(kr, table, meta.tok_pos)
+        for t in range(T):
+            p, slot = int(meta.tok_pos[t]), int(meta.tok_slot[t])
+            page = int(view.page_table[slot, p // view.page_size])
+            view.k[page, 0, p % view.page_size, :] = 0
+            view.k[page, 0, p % view.page_size, :C] = c[t].to(view.k.dtype)
+            view.k[page, 0, p % view.page_size, C:C + R] = kr[t, 0].to(view.k.dtype)
+        return q.reshape(T, H * (D + R)).to(self.dtype)
+
+    def retention(self, proj, p, state, meta):
+        H, D, Dv = p.n_heads, p.head_dim, p.value_dim
+        at = p.offsets()
+        x = proj.float()
+        T = x.shape[0]
+        q = x[:, at["q"]:at["q"] + H * D].reshape(T, H, D).clone()
+        k = x[:, at["k"]:at["k"] + H * D].reshape(T, H, D).clone()
+        v = x[:, at["v"]:at["v"] + H * Dv].reshape(T, H, Dv)
+        table = p.position.table() if hasattr(p.position, "table") else None
+        if table is not None:
+            self._turn(q, table, meta.tok_pos)
+            self._turn(k, table, meta.tok_pos)
+        q = q * D ** -0.5
+        decay = p.decays.view(H, D)
+        o = torch.zeros(T, H, Dv)
+        for first, n, slot in self._runs(meta):
+            S = state["S"][slot].clone()                                        # [H, Dv, D]
+            for t in range(first, first + n):
+                S = S * decay[:, None, :] + v[t][:, :, None] * k[t][:, None, :]
+                o[t] = torch.einsum("hvd,hd->hv", S, q[t])
+            state["S"][slot] = S
+        o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + p.norm_eps)
+        gate = x[:, at["g"]:at["g"] + H * Dv]
+        return (o.reshape(T, H * Dv) * (gate / (1.0 + torch.exp(-gate)))).to(self.dtype)
 
     def gather_rows(self, x, rows):
         return x[rows.long()].clone()
