@@ -17,7 +17,8 @@ template <typename T, int EPL>
 __global__ void __launch_bounds__(128) attn_simple_kernel(T* __restrict__ out, const T* __restrict__ q,
                                                          RbPagedLayer cache, const int* __restrict__ tok_pos,
                                                          const int* __restrict__ tok_slot, int n_tokens, int H,
-                                                         float scale, int window) {
+                                                         float scale, int window, const float* __restrict__ sinks,
+                                                         float softcap) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -39,6 +40,8 @@ __global__ void __launch_bounds__(128) attn_simple_kernel(T* __restrict__ out, c
     acc[e] = 0.f;
   }
   float m = -INFINITY, l = 0.f;
+  if (sinks != nullptr) { m = sinks[h]; l = 1.f; }     // the sink: one more term of the denominator, without a value
+  const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   for (int p = lo; p <= pos; ++p) {
     const int64_t off = rb_page_offset(cache, slot, p, kvh);
@@ -48,7 +51,8 @@ __global__ void __launch_bounds__(128) attn_simple_kernel(T* __restrict__ out, c
       const int d = lane + 32 * e;
       if (d < D) part = fmaf(qr[e], rb_to_float<T>(Kb[off + d]), part);
     }
-    const float s = rb_warp_sum(part) * scale;
+    float s = rb_warp_sum(part) * scale;
+    if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
     const float mn = fmaxf(m, s);
     const float corr = expf(m - mn);   // exp(-inf) = 0 on the first key
     const float pe = expf(s - mn);
@@ -72,12 +76,13 @@ __global__ void __launch_bounds__(128) attn_simple_kernel(T* __restrict__ out, c
 template <typename T>
 int launch(T* out, const T* q, RbPagedLayer c, const int* tok_pos, const int* tok_slot, int n_tokens, int H,
            float scale, int window, cudaStream_t stream) {
+  const RbAttentionOptions opt = rb_attention_take();
   const int64_t warps = (int64_t)n_tokens * H;
   const int blocks = (int)((warps + 3) / 4);
   int epl = (c.head_dim + 31) / 32;
   if (epl > 8) epl = epl <= 12 ? 12 : (epl <= 16 ? 16 : (epl <= 24 ? 24 : (epl <= 32 ? 32 : epl)));   // head sizes up to 1,024
 #define CASE(E) \
-  case E: RB_LAUNCH("attn_simple_kernel", (attn_simple_kernel<T, E>), blocks, 128, 0, stream, out, q, c, tok_pos, tok_slot, n_tokens, H, scale, window); break;
+  case E: RB_LAUNCH("attn_simple_kernel", (attn_simple_kernel<T, E>), blocks, 128, 0, stream, out, q, c, tok_pos, tok_slot, n_tokens, H, scale, window, opt.sinks, opt.softcap); break;
   switch (epl) {
     CASE(1) CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8) CASE(12) CASE(16) CASE(24) CASE(32)
     default: RB_FAIL("rb_attention_simple: head_dim %d exceeds 1024", c.head_dim);
@@ -88,6 +93,22 @@ int launch(T* out, const T* q, RbPagedLayer c, const int* tok_pos, const int* to
 }
 
 }  // namespace
+
+static thread_local RbAttentionOptions t_next_attention;
+
+RbAttentionOptions rb_attention_take() {
+  const RbAttentionOptions o = t_next_attention;
+  t_next_attention = RbAttentionOptions();
+  return o;
+}
+
+// For the calling thread's next attention launch (any of the library's attention entry points that takes them:
+// rb_attention_simple, rb_attention_prefill, rb_attention_decode); see rb_common.cuh.
+RB_EXPORT int rb_attention_next(const float* sinks, float softcap) {
+  t_next_attention.sinks = sinks;
+  t_next_attention.softcap = softcap > 0.f ? softcap : 0.f;
+  return 0;
+}
 
 RB_EXPORT int rb_attention_simple(void* out, const void* q, int dtype, const void* cache_k, const void* cache_v,
                                   const int* page_table, int max_pages, int page_size, const int* tok_pos,

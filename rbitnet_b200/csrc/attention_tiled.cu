@@ -63,6 +63,9 @@ struct AttnParams {
   int H, G;
   float scale_log2;         // scale * log2(e)
   int window;               // 0: none
+  const float* sinks;       // [H] or null: a term exp(sinks[h]) in head h's denominator
+  float softcap;            // > 0: score <- softcap * tanh(score * scale / softcap)
+  float scale;
   float* part_o;            // decode: [T, H, n_splits, D]
   float* part_ml;           // decode: [T, H, n_splits, 2]
   int n_splits;
@@ -169,6 +172,18 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
 #pragma unroll
   for (int i = 0; i < DT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  if (p.sinks != nullptr && (!DECODE || (warp == 0 && blockIdx.z == 0))) {
+    // the sink counts once per row: in the sums of one thread of the row's quad, and (decode) of one warp of one part
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = rb + g + 8 * h;
+      if (r < n_rows) {
+        m_run[h] = p.sinks[kvh * G + r % G] * 1.4426950408889634f;
+        l_run[h] = t4 == 0 ? 1.f : 0.f;
+      }
+    }
+  }
+  const float cap_log2 = p.softcap * 1.4426950408889634f, scale_over_cap = p.softcap > 0.f ? p.scale / p.softcap : 0.f;
   // rows g and g+8 of this warp: their positions and validity
   int row_pos[2], row_lo[2];
   bool row_ok[2];
@@ -224,7 +239,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
           const int h = c >> 1;
           const int key = key_base + nt * 8 + t4 * 2 + (c & 1);
           const bool ok = row_ok[h] && key <= row_pos[h] && key >= row_lo[h];
-          const float v = ok ? s[nt][c] * p.scale_log2 : -INFINITY;
+          const float v = !ok ? -INFINITY : (p.softcap > 0.f ? cap_log2 * tanhf(s[nt][c] * scale_over_cap) : s[nt][c] * p.scale_log2);
           s[nt][c] = v;
           m_new[h] = fmaxf(m_new[h], v);
         }
@@ -440,6 +455,7 @@ RB_EXPORT int rb_attention_prefill(void* out, const void* q, const void* cache_k
   p.cache = RbPagedLayer{(void*)cache_k, (void*)cache_v, page_table, max_pages, page_size, Kh, D};
   p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.tile_tok0 = tile_tok0; p.tile_ntok = tile_ntok;
   p.H = H; p.G = H / Kh; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+  { const RbAttentionOptions opt = rb_attention_take(); p.sinks = opt.sinks; p.softcap = opt.softcap; p.scale = scale; }
   p.part_o = nullptr; p.part_ml = nullptr; p.n_splits = 1;
   return launch_d<false>(D, p, dim3(n_tiles, Kh, 1), stream);
 }
@@ -489,6 +505,7 @@ RB_EXPORT int rb_attention_decode(void* out, const void* q, const void* cache_k,
   p.cache = RbPagedLayer{(void*)cache_k, (void*)cache_v, page_table, max_pages, page_size, Kh, D};
   p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.tile_tok0 = nullptr; p.tile_ntok = nullptr;
   p.H = H; p.G = H / Kh; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+  { const RbAttentionOptions opt = rb_attention_take(); p.sinks = opt.sinks; p.softcap = opt.softcap; p.scale = scale; }
   p.part_o = part_o; p.part_ml = part_ml; p.n_splits = n_splits;
   if (launch_d<true>(D, p, dim3(B, Kh, n_splits), stream) != 0) return -1;
   if (n_splits > 1) return rb_attention_combine(out, part_o, part_ml, B, H, D, n_splits, stream);

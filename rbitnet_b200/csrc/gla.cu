@@ -63,7 +63,8 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(float* __restrict__ o, co
                                                        int q_off, int k_off, int v_off, const float* __restrict__ alpha,
                                                        float q_scale, float* __restrict__ state,
                                                        const int* __restrict__ seq_first, const int* __restrict__ seq_count,
-                                                       const int* __restrict__ tok_slot, int H, int D, int Dv) {
+                                                       const int* __restrict__ tok_slot, int H, int D, int Dv,
+                                                       int64_t a_ld) {
   rb_pdl_launch_dependents();
   constexpr int COLS = 128 / P;                    // value columns of a block
   constexpr int DP = P * GLA_R;                    // channels with padding
@@ -90,7 +91,7 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(float* __restrict__ o, co
       const bool in = d < D;
       s_q[i][d] = in ? rows[row + q_off + head * D + d] * q_scale : 0.f;
       s_k[i][d] = in ? rows[row + k_off + head * D + d] : 0.f;
-      s_a[i][d] = in ? alpha[(int64_t)(first + t0 + i) * H * D + head * D + d] : 0.f;
+      s_a[i][d] = in ? alpha[(int64_t)(first + t0 + i) * a_ld + head * D + d] : 0.f;
     }
     for (int e = threadIdx.x; e < nt * COLS; e += blockDim.x) {
       const int i = e / COLS, c = e % COLS;
@@ -124,12 +125,12 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(float* __restrict__ o, co
 template <int P>
 int launch_scan(float* o, const float* rows, int64_t ld, int q_off, int k_off, int v_off, const float* alpha, float q_scale,
                 float* state, const int* seq_first, const int* seq_count, const int* tok_slot, int n_runs, int H, int D,
-                int Dv, cudaStream_t stream) {
+                int Dv, int64_t a_ld, cudaStream_t stream) {
   constexpr int COLS = 128 / P;
   const dim3 grid(n_runs, H, (Dv + COLS - 1) / COLS);
   RB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "rb_gla_scan: %d heads of %d value columns are too many for one launch", H, Dv);
   RB_LAUNCH("gla_scan_kernel", (gla_scan_kernel<P>), grid, 128, 0, stream, o, rows, ld, q_off, k_off, v_off, alpha, q_scale,
-            state, seq_first, seq_count, tok_slot, H, D, Dv);
+            state, seq_first, seq_count, tok_slot, H, D, Dv, a_ld);
   RB_CHECK_LAUNCH("rb_gla_scan");
   return 0;
 }
@@ -166,7 +167,8 @@ __global__ void __launch_bounds__(128) gla_chunk_prepare_kernel(float* __restric
                                                                 int64_t ld, int q_off, int k_off,
                                                                 const float* __restrict__ log_alpha, float q_scale,
                                                                 const int* __restrict__ chunk_row,
-                                                                const int* __restrict__ chunk_len, int H, int D) {
+                                                                const int* __restrict__ chunk_len, int H, int D,
+                                                                int64_t a_ld) {
   rb_pdl_launch_dependents();
   extern __shared__ __align__(16) float s_gprep[];
   const int KS = D + 4;                          // row stride: the lanes' 16-byte loads of their own rows spread over the banks
@@ -183,7 +185,7 @@ __global__ void __launch_bounds__(128) gla_chunk_prepare_kernel(float* __restric
     float4 bb = make_float4(0.f, 0.f, 0.f, 0.f), qq = bb, kk = bb;
     if (j < m) {
       const float* row = rows + (int64_t)(row0 + j) * ld;
-      bb = *reinterpret_cast<const float4*>(log_alpha + ((int64_t)(row0 + j) * H + h) * D + d);
+      bb = *reinterpret_cast<const float4*>(log_alpha + (int64_t)(row0 + j) * a_ld + h * D + d);
       qq = *reinterpret_cast<const float4*>(row + q_off + h * D + d);
       kk = *reinterpret_cast<const float4*>(row + k_off + h * D + d);
       qq.x *= q_scale; qq.y *= q_scale; qq.z *= q_scale; qq.w *= q_scale;
@@ -374,17 +376,31 @@ RB_EXPORT int rb_gla_decay(float* alpha, const float* rows, int64_t ld, int a_of
 
 RB_EXPORT int rb_gla_max_dim() { return 32 * GLA_R; }
 
+// Decays that do not depend on the token (a fixed decay per head, say): after rb_gla_shared_decays() the calling
+// thread's next rb_gla_scan or rb_gla_chunked reads ONE row [H * D] of decays (or of their logarithms) for every token.
+static thread_local bool t_shared_decays = false;
+static bool take_shared_decays() {
+  const bool v = t_shared_decays;
+  t_shared_decays = false;
+  return v;
+}
+RB_EXPORT int rb_gla_shared_decays() {
+  t_shared_decays = true;
+  return 0;
+}
+
 // o [T, H, Dv] float32.  n_runs runs (seq_first, seq_count; null: every one of the n_runs rows is its own run).
 // state: [n_slots, H, Dv, D] float32.
 RB_EXPORT int rb_gla_scan(float* o, const float* rows, int64_t ld, int q_off, int k_off, int v_off, const float* alpha,
                           float q_scale, float* state, const int* seq_first, const int* seq_count, const int* tok_slot,
                           int n_runs, int H, int D, int Dv, cudaStream_t stream) {
+  const int64_t a_ld = take_shared_decays() ? 0 : (int64_t)H * D;
   if (n_runs == 0) return 0;
   RB_REQUIRE(H > 0 && D > 0 && Dv > 0 && D <= 32 * GLA_R, "rb_gla_scan: bad sizes H=%d D=%d Dv=%d (at most %d key channels)", H,
              D, Dv, 32 * GLA_R);
   int P = 1;
   while (P * GLA_R < D) P *= 2;
-#define GO(PP) return launch_scan<PP>(o, rows, ld, q_off, k_off, v_off, alpha, q_scale, state, seq_first, seq_count, tok_slot, n_runs, H, D, Dv, stream)
+#define GO(PP) return launch_scan<PP>(o, rows, ld, q_off, k_off, v_off, alpha, q_scale, state, seq_first, seq_count, tok_slot, n_runs, H, D, Dv, a_ld, stream)
   switch (P) {
     case 1: GO(1);
     case 2: GO(2);
@@ -412,6 +428,7 @@ RB_EXPORT int rb_gla_chunked(float* o, const float* rows, int64_t ld, int q_off,
                              float q_scale, float* state, float* scratch, const int* seq_first, const int* seq_count,
                              const int* run_chunk0, const int* chunk_row, const int* chunk_len, const int* tok_slot,
                              int n_runs, int n_chunks, int H, int D, int Dv, cudaStream_t stream) {
+  const int64_t a_ld = take_shared_decays() ? 0 : (int64_t)H * D;
   if (n_runs == 0 || n_chunks == 0) return 0;
   RB_REQUIRE(H > 0 && H <= 65535 && rb_gla_chunked_supports(D, Dv, ld, q_off, k_off, v_off) && (uintptr_t)rows % 16 == 0 &&
                  (uintptr_t)scratch % 16 == 0 && (uintptr_t)log_alpha % 16 == 0,
@@ -425,7 +442,7 @@ RB_EXPORT int rb_gla_chunked(float* o, const float* rows, int64_t ld, int q_off,
   }
   RB_REQUIRE(smem_a <= 64 * 1024 && smem_b <= 128 * 1024, "rb_gla_chunked: key size %d needs too much shared memory", D);
   RB_LAUNCH("gla_chunk_prepare_kernel", (gla_chunk_prepare_kernel), dim3(n_chunks, H), 128, smem_a, stream, scratch, rows, ld,
-            q_off, k_off, log_alpha, q_scale, chunk_row, chunk_len, H, D);
+            q_off, k_off, log_alpha, q_scale, chunk_row, chunk_len, H, D, a_ld);
   RB_CHECK_LAUNCH("rb_gla_chunked");
   const dim3 grid(n_runs, H, (Dv + GCT - 1) / GCT);
   RB_REQUIRE(grid.z <= 65535, "rb_gla_chunked: too many columns");

@@ -173,6 +173,18 @@ struct RbPagedLayer {
   int head_dim;
 };
 
+// ---------------------------------------------------------------- options of the next attention call
+// rb_attention_next(sinks, softcap) (attention_simple.cu) sets them for the calling thread's next attention launch,
+// which takes them with rb_attention_take (and so clears them):
+//   sinks    float32 [H] or null: the softmax's denominator of head h also holds exp(sinks[h]) (no key, no value,
+//            not scaled, counted once)
+//   softcap  > 0: score <- softcap * tanh(score / softcap), after the scale and before the softmax
+struct RbAttentionOptions {
+  const float* sinks = nullptr;
+  float softcap = 0.f;
+};
+RbAttentionOptions rb_attention_take();
+
 // ---------------------------------------------------------------- the checked build
 // With -DRB_CHECKED (RBITNET_CHECKED=1 when the library is built) every cache address that goes
 // through rb_page_offset is checked first: a slot, position or kv head outside what the layer holds

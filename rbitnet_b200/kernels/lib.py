@@ -87,6 +87,15 @@ _SIGNATURES = {
     "rb_attention_prefill_tc": [P, P, P, P, L, P, I, I, P, P, P, P, I, I, I, I, F, I, P],
     "rb_attention_decode_tma": [P, P, P, P, L, P, I, I, P, P, I, I, I, I, F, I, P, P, I, P],
     "rb_attention_decode_static": [P, P, P, P, P, I, I, P, P, I, I, I, I, F, I, I, P],
+    "rb_attention_next": [P, F],
+    "rb_gla_shared_decays": [],
+    "rb_round_rows": [P, I, P, L, P],
+    "rb_norm_add": [P, P, P, F, I, I, P, I, P],
+    "rb_token_gate": [P, I, P, L, P, I, P, I, I, P],
+    "rb_embed_pairs": [P, P, P, I, P, P, P, P, I, I, I, F, I, I, I, I, P],
+    "rb_qk_prepare": [P, P, I, P, L, P, I, P, P, I, P, P, F, P, F, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, L, F, I, P],
+    "rb_latent_rotate_append": [P, I, P, L, P, F, P, F, I, P, P, P, P, I, I, I, I, I, I, I, I, P],
+    "rb_rotate_rows": [P, L, I, I, I, P, F, I, I, P, I, P],
     "rb_set_error_flag_for_test": [I],
     "rb_wait_probe": [L, I, P, P],
     "rb_count_wait_probe": [P, L, I, P, P],
@@ -94,7 +103,7 @@ _SIGNATURES = {
 
 
 #: source files whose kernels address the cache through the checked function (each has its own word)
-CHECKED_FILES = ("elementwise", "gemm_tcgen05", "attention_simple", "attention_tiled", "latent")
+CHECKED_FILES = ("elementwise", "gemm_tcgen05", "attention_simple", "attention_tiled", "latent", "prepare")
 
 
 class KernelError(RuntimeError):

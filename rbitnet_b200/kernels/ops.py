@@ -451,15 +451,24 @@ class CudaOps:
         return z
 
     def attention(self, q: torch.Tensor, meta, view, n_heads: int, scale: float,
-                  window: Optional[int]) -> torch.Tensor:
-        """Each new token's queries over its sequence's cached keys up to its own position."""
+                  window: Optional[int], sinks: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
+        """Each new token's queries over its sequence's cached keys up to its own position.  ``sinks`` (float32 [H]):
+        head h's softmax denominator also holds exp(sinks[h]); ``softcap`` > 0: score <- softcap * tanh(score /
+        softcap).  With either, the kernels that know them run: the mma.sync prefill and split decode kernels in
+        bfloat16 (head sizes they take), else the plain kernel."""
         T, H, D = q.shape
         Kh = view.n_kv_heads
         out = torch.empty((T, H * D), dtype=self.dtype, device=self.device)
         win = int(window or 0)
+        optioned = sinks is not None or softcap > 0.0
+        if optioned:
+            if sinks is not None:
+                self._check(sinks, torch.float32, "attention sinks")
+            self.lib.call("rb_attention_next", _ptr(sinks), float(softcap), launches=0)
         if self.dtype == torch.bfloat16 and meta.single_token and \
                 self.lib.raw("rb_attention_tiled_supports")(H, Kh, D, view.page_size, 1):
-            on_tma = self.decode_on_tma and self.lib.raw("rb_attention_decode_tma_supports")(H, Kh, D, view.page_size)
+            on_tma = self.decode_on_tma and not optioned and \
+                self.lib.raw("rb_attention_decode_tma_supports")(H, Kh, D, view.page_size)
             if on_tma:
                 n_splits = self.lib.raw("rb_attention_decode_tma_parts")(T * Kh, max(1, -(-meta.max_context // 64)), D)
             else:
@@ -482,7 +491,7 @@ class CudaOps:
                               _ptr(view.page_table), view.max_pages, view.page_size, _ptr(meta.tok_pos),
                               _ptr(meta.tok_slot), T, H, Kh, D, float(scale), win, _ptr(part_o), _ptr(part_ml),
                               n_splits, self._stream(), launches=2 if n_splits > 1 else 1)
-        elif self.dtype == torch.bfloat16 and self.prefill_on_tcgen05 and \
+        elif self.dtype == torch.bfloat16 and self.prefill_on_tcgen05 and not optioned and \
                 self.lib.raw("rb_attention_prefill_tc_supports")(H, Kh, D, view.page_size):
             tok0, ntok, n_tiles = self._prefill_tiles(meta, 128 // (H // Kh))
             self.lib.call("rb_attention_prefill_tc", _ptr(out), _ptr(q), _ptr(view.k), _ptr(view.v),
@@ -856,6 +865,152 @@ class CudaOps:
                           launches=2)
         else:
             self.lib.call("rb_gla_scan", _ptr(o), _ptr(proj), proj.stride(0), at["q"], at["k"], at["v"], _ptr(alpha),
+                          float(D) ** -0.5, _ptr(state["S"]), _ptr(first), _ptr(count), _ptr(meta.tok_slot), n_runs, H, D, Dv,
+                          self._stream())
+        out = torch.empty((T, H * Dv), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_head_norm_gate", _ptr(out), self.code, _ptr(o), _ptr(p.norm_w), _ptr(proj), proj.stride(0), F32,
+                      at["g"], T, H, Dv, float(p.norm_eps), 1, 1, self._stream())
+        return out
+
+    # ------------------------------------------------------------------ sublayers that read the residual stream itself
+    def round_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """The float32 rows in the compute dtype (the rows themselves where that is float32)."""
+        self._check(x, torch.float32, "round_rows rows")
+        if self.dtype == torch.float32:
+            return x
+        out = torch.empty(x.shape, dtype=self.dtype, device=self.device)
+        self.lib.call("rb_round_rows", _ptr(out), self.code, _ptr(x), x.numel(), self._stream())
+        return out
+
+    def norm_add(self, x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, want_rounded: bool = False):
+        """x += y / rms(y) * w, row by row in float32 (y: a sublayer's float32 result).  ``want_rounded``: the new rows
+        are also returned in the compute dtype, from the same kernel."""
+        self._check(x, torch.float32, "norm_add target")
+        self._check(y, torch.float32, "norm_add result")
+        T, E = x.shape
+        if y.shape != x.shape or w.shape[0] != E:
+            raise KernelError(f"norm_add: shapes {tuple(x.shape)}, {tuple(y.shape)}, {tuple(w.shape)}")
+        rounded = None
+        if want_rounded and self.dtype != torch.float32:
+            rounded = torch.empty((T, E), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_norm_add", _ptr(x), _ptr(y), _ptr(w), float(eps), T, E, _ptr(rounded), self.code, self._stream())
+        if not want_rounded:
+            return None
+        return x if rounded is None else rounded
+
+    def token_gate(self, a: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """gelu_tanh(a[t]) * table[ids[t]] -> [T, dim] in the compute dtype (a: float32 [T, dim])."""
+        self._check(a, torch.float32, "token_gate rows")
+        self._check(table, self.dtype, "token_gate table")
+        T, dim = a.shape
+        out = torch.empty((T, dim), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_token_gate", _ptr(out), self.code, _ptr(a), a.stride(0), _ptr(table), self.code, _ptr(ids), T, dim,
+                      self._stream())
+        return out
+
+    def embed_pairs(self, meta, table: torch.Tensor, scale: float, pair_table: torch.Tensor, pair_hash,
+                    previous: torch.Tensor) -> torch.Tensor:
+        """float32 rows table[id] * scale + pair_table[(previous id * a + id * b) mod n] with (n, a, b) = ``pair_hash``;
+        a sequence's first token takes row n.  ``previous`` (int32 [n_slots, 1]) holds every sequence's last token and
+        moves on."""
+        T, (V, E) = meta.n_tokens, table.shape
+        buckets, mul_prev, mul_cur = pair_hash
+        out = torch.empty((T, E), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_embed_pairs", _ptr(out), _ptr(table), _ptr(pair_table), _CODE[table.dtype], _ptr(meta.token_ids),
+                      _ptr(meta.tok_pos), _ptr(meta.tok_slot), _ptr(previous), T, E, V, float(scale), int(buckets),
+                      int(mul_prev), int(mul_cur), 1 if meta.single_token else 0, self._stream(),
+                      launches=1 if meta.single_token else 2)
+        return out
+
+    def qk_prepare(self, proj: torch.Tensor, meta, view, n_heads: int, head_dim: int, value_dim: int, table, norm,
+                   q_norm_w, k_norm_w, eps: float, conv=None, tail=None, values_are_keys: bool = False, v_mix=None,
+                   gate_heads: bool = False):
+        """From float32 rows [q | k | v (unless ``values_are_keys``) | a gate logit per head (if ``gate_heads``)]:
+        ``conv`` ([(H + Kh) D, taps] float32): a causal convolution over time on the q and k channels, whose last
+        rows per sequence live in ``tail`` (a ring by position); ``norm`` "projection" (weights [H D], [Kh D]) or
+        "head_weight" (one [D] for all q heads, one for all k heads): RMS norms before the rotation; the rotation of
+        ``table``; k and v into the cache (v: own, or (1 - l) v + l other[:, at:] with ``v_mix`` = (l, other, at), or
+        the keys as they leave the convolution).  Returns (q [T, H, cache width], gate logits [T, H] or None), both in
+        the compute dtype."""
+        self._check(proj, torch.float32, "qk_prepare projections")
+        T, Dc, Kh = proj.shape[0], view.head_dim, view.n_kv_heads
+        if table is None:
+            freq, magnitude, interleaved, rot_dim = None, 1.0, True, 0
+        else:
+            freq, magnitude, interleaved, rot_dim = table
+        mode = {None: 0, "projection": 1, "head_weight": 2}[norm]
+        K = conv.shape[1] if conv is not None else 0
+        first = count = tok_first = None
+        if conv is not None and K > 1:
+            first, count, tok_first, n_runs = self._runs(meta)
+        q = torch.empty((T, n_heads, Dc), dtype=self.dtype, device=self.device)
+        gates = torch.empty((T, n_heads), dtype=self.dtype, device=self.device) if gate_heads else None
+        lam, other, at = v_mix if v_mix is not None else (0.0, None, 0)
+        mix_ptr = c_void_p(other.data_ptr() + at * 4) if other is not None else c_void_p(0)
+        self.lib.call("rb_qk_prepare", _ptr(q), _ptr(gates), self.code, _ptr(proj), proj.stride(0), _ptr(conv), K, _ptr(tail),
+                      _ptr(tok_first), mode, _ptr(q_norm_w), _ptr(k_norm_w), float(eps), _ptr(freq), float(magnitude),
+                      rot_dim, 1 if interleaved else 0, _ptr(meta.tok_pos), _ptr(meta.tok_slot), _ptr(view.k), _ptr(view.v),
+                      _ptr(view.page_table), view.max_pages, view.page_size, T, n_heads, Kh, head_dim, value_dim, Dc,
+                      1 if values_are_keys else 0, mix_ptr, other.stride(0) if other is not None else 0, float(lam),
+                      1 if gate_heads else 0, self._stream())
+        if first is not None:
+            # runs of several rows: the ring moves on to each run's end after every row has read it
+            C = (n_heads + Kh) * head_dim
+            self.lib.call("rb_conv_tail_update", _ptr(tail), _ptr(proj), proj.stride(0), 0, F32, c_void_p(0), _ptr(first),
+                          _ptr(count), _ptr(meta.tok_slot), _ptr(meta.tok_pos), n_runs, C, K, self._stream())
+        return q, gates
+
+    def latent_rotate_append(self, down: torch.Tensor, n_heads: int, head_dim: int, rot_dim: int, kv_rank: int, table,
+                             w: torch.Tensor, eps: float, meta, view) -> torch.Tensor:
+        """From float32 rows [H query heads of head_dim + rot_dim | latent of kv_rank | key part of rot_dim]: the
+        latent under its RMS norm and weight and the key part turned by position go to the sequence's page as
+        [c | k_r | zeros]; the queries are returned ([T, H (head_dim + rot_dim)], compute dtype) with their last
+        rot_dim values turned."""
+        self._check(down, torch.float32, "latent_rotate_append rows")
+        T = down.shape[0]
+        freq, magnitude, interleaved = None, 1.0, True
+        if rot_dim:
+            freq, magnitude, interleaved, turned = table
+            if turned != rot_dim:
+                raise KernelError("latent_rotate_append: the position encoding turns the whole key part")
+        q = torch.empty((T, n_heads * (head_dim + rot_dim)), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_latent_rotate_append", _ptr(q), self.code, _ptr(down), down.stride(0), _ptr(w), float(eps),
+                      _ptr(freq), float(magnitude), 1 if interleaved else 0, _ptr(meta.tok_pos), _ptr(meta.tok_slot),
+                      _ptr(view.k), _ptr(view.page_table), view.max_pages, view.page_size, view.head_dim, T, n_heads,
+                      head_dim, rot_dim, kv_rank, self._stream())
+        return q
+
+    def retention(self, proj: torch.Tensor, p, state, meta) -> torch.Tensor:
+        """The recurrence of ``parts.retention.Retention`` ``p`` on float32 rows [q | k | v | g] of its stacked
+        projection: q and k turned by position (in place), the memory's steps with the heads' fixed decays (gated
+        linear attention's kernels on one shared row of decays), each head's outputs divided by their root mean square
+        and multiplied by silu(g), as [T, H * value_dim] in the compute dtype.  ``state["S"]`` moves on."""
+        self._check(proj, torch.float32, "retention projections")
+        T, H, D, Dv = proj.shape[0], p.n_heads, p.head_dim, p.value_dim
+        if D > self.lib.raw("rb_gla_max_dim")():
+            raise KernelError(f"retention: {D} key channels per head are more than the kernel holds")
+        at = p.offsets()
+        table = p.position.table() if hasattr(p.position, "table") else None
+        if table is not None:
+            freq, magnitude, interleaved, rot_dim = table
+            # q heads and k heads are neighbours in a row: 2 H heads of D from column 0
+            self.lib.call("rb_rotate_rows", _ptr(proj), proj.stride(0), at["q"], 2 * H, D, _ptr(freq), float(magnitude),
+                          rot_dim, 1 if interleaved else 0, _ptr(meta.tok_pos), T, self._stream())
+        first, count, _, n_runs = self._runs(meta)
+        chunked = first is not None and self.gla_in_chunks and \
+            self.lib.raw("rb_gla_chunked_supports")(D, Dv, proj.stride(0), at["q"], at["k"], at["v"])
+        o = torch.empty((T, H * Dv), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_gla_shared_decays", launches=0)
+        if chunked:
+            run_chunk0, chunk_row, chunk_len, n_chunks = self._delta_chunks(meta)
+            scratch = torch.empty((n_chunks * H * self.lib.raw("rb_gla_chunk_floats")(D),), dtype=torch.float32,
+                                  device=self.device)
+            self.lib.call("rb_gla_chunked", _ptr(o), _ptr(proj), proj.stride(0), at["q"], at["k"], at["v"], _ptr(p.log_decays),
+                          float(D) ** -0.5, _ptr(state["S"]), _ptr(scratch), _ptr(first), _ptr(count), _ptr(run_chunk0),
+                          _ptr(chunk_row), _ptr(chunk_len), _ptr(meta.tok_slot), n_runs, n_chunks, H, D, Dv, self._stream(),
+                          launches=2)
+        else:
+            self.lib.call("rb_gla_scan", _ptr(o), _ptr(proj), proj.stride(0), at["q"], at["k"], at["v"], _ptr(p.decays),
                           float(D) ** -0.5, _ptr(state["S"]), _ptr(first), _ptr(count), _ptr(meta.tok_slot), n_runs, H, D, Dv,
                           self._stream())
         out = torch.empty((T, H * Dv), dtype=self.dtype, device=self.device)
