@@ -546,6 +546,30 @@ def _nifarax_shape(width, mem_heads, mem_dim, mem_vdim, heads, dim, q_rank, kv_r
             "logit_softcap": 30.0, "max_positions": 8192, "layers": ls}
 
 
+def _gozotar_shape(width, heads, kv, dim, vdim, lat_heads, lat_dim, lat_rot, kv_rank, ret_heads, ret_dim, ret_vdim, ff, layers,
+                   vocab=32000, side=256):
+    """Layer sizes in the manner of a real model: of every three layers the first is attention through latents with a
+    turned key part and sinks, the second grouped attention with normed heads, capped scores and mixed values, the third
+    grouped attention behind short convolutions beside retention; dense feed-forwards, the pair embedding and the side
+    embedding everywhere."""
+    mlp = {"kind": "dense", "ff": ff}
+    lat = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": lat_heads, "dim": lat_dim, "rot_dim": lat_rot, "vdim": lat_dim, "kv_rank": kv_rank,
+        "scale": (lat_dim + lat_rot) ** -0.5, "rot": {"base": 10000.0, "dims": lat_rot}}}
+    att = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "softcap": 50.0, "v_mix": True,
+        "rot": {"base": 500000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    par = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "conv": 4,
+                 "rot": {"base": 10000.0, "dims": dim // 2}},
+        "right": {"heads": ret_heads, "dim": ret_dim, "vdim": ret_vdim, "rot": {"base": 10000.0, "dims": ret_dim},
+                  "decay": [1.0 - 2.0 ** (-5 - 3 * i / max(ret_heads - 1, 1)) for i in range(ret_heads)]},
+        "left_scale": 0.5, "right_scale": 0.5}}
+    return {"architecture": "Gozotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "max_positions": 8192,
+            "embedding": {"bigram": {"buckets": 100003, "mul_prev": 36313, "mul_cur": 27191}}, "token_side": {"dim": side},
+            "layers": [dict((lat, att, par)[i % 3]) for i in range(layers)]}
+
+
 DESIGN_SIZES = {
     # name: (the design's configuration, the configuration of equal width, layer runs and feed-forward size beside it)
     "w2048": (_safuvik_shape(2048, 16, 4, 128, 64, 1024, 16, 8, 128, 256, 5632, 6), _llama_like(2048, 16, 4, 128, 5632, 6)),
@@ -558,6 +582,11 @@ DESIGN_SIZES = {
                       _vaderax_shape(2048, 16, 4, 128, 16, 8, 128, 128, 5632, 30, 4, 1408, 4)),
     "nifarax_w4096": (_nifarax_shape(4096, 16, 128, 256, 32, 128, 1536, 256, 64, 8, 1792, 1792, 3),
                       _vaderax_shape(4096, 32, 8, 128, 32, 16, 128, 128, 14336, 62, 8, 1792, 3)),
+    # Gozotar beside Nifarax (attention through latents and a matrix memory with decays both): 6 layers beside 6 runs, 3 beside 3
+    "gozotar_w2048": (_gozotar_shape(2048, 16, 4, 128, 128, 16, 128, 64, 512, 8, 128, 256, 5632, 6),
+                      _nifarax_shape(2048, 8, 128, 256, 16, 128, 768, 128, 32, 4, 1408, 1408, 6)),
+    "gozotar_w4096": (_gozotar_shape(4096, 32, 8, 128, 128, 32, 128, 64, 512, 16, 128, 256, 14336, 3),
+                      _nifarax_shape(4096, 16, 128, 256, 32, 128, 1536, 256, 64, 8, 1792, 1792, 3)),
 }
 
 
@@ -566,7 +595,8 @@ class DesignTimer(KernelTimer):
     OPS = KernelTimer.OPS + ("stream_step", "normed_mean", "streams_expand", "streams_sum", "norm_rotate_append", "head_gate",
                              "gated_recurrence", "matrix_memory", "layernorm", "add_rows", "gated_delta", "route", "routed_experts",
                              "rmsnorm_grouped", "input_filter", "gated_add", "add_scaled_rows", "softcap", "gated_linear_attention",
-                             "latent_norm_append", "per_head_linear", "route_scored")
+                             "latent_norm_append", "per_head_linear", "route_scored", "qk_prepare", "latent_rotate_append",
+                             "retention", "norm_add", "round_rows", "token_gate", "embed_pairs")
 
     @staticmethod
     def _describe(name, a, kw, sync=True):
@@ -608,6 +638,29 @@ class DesignTimer(KernelTimer):
             return (f"gated linear attention: decays, recurrence, head norm and gate [{T} rows, {p.n_heads} heads of "
                     f"{p.head_dim}x{p.value_dim}]",
                     T * (2 * p.n_heads * p.head_dim + 2 * p.n_heads * p.value_dim + p.decay_rank) * 4 + T * p.n_heads * p.value_dim * 2, 0.0)
+        if name == "qk_prepare":
+            proj, view, H = a[0], a[2], a[3]
+            T = proj.shape[0]
+            return (f"q/k convolution, norm, rotation, values + append [{T} rows of {proj.shape[1]}]",
+                    el(proj) + T * (H + 2 * view.n_kv_heads) * view.head_dim * 2, 0.0)
+        if name == "latent_rotate_append":
+            down, H, D, R = a[0], a[1], a[2], a[3]
+            T = down.shape[0]
+            return f"latent's norm, turned parts + append [{T} rows of {down.shape[1]}]", el(down) + T * (H * (D + R) + a[9].head_dim) * 2, 0.0
+        if name == "retention":
+            proj, p = a[0], a[1]
+            T = proj.shape[0]
+            return (f"retention: rotation, recurrence, head norm and gate [{T} rows, {p.n_heads} heads of {p.head_dim}x{p.value_dim}]",
+                    el(proj) + T * p.n_heads * p.value_dim * 2, 0.0)
+        if name == "norm_add":
+            return f"normed result added to the residual stream [{a[0].shape[0]} rows]", 3 * el(a[0]) + a[0].numel() * 2, 0.0
+        if name == "round_rows":
+            return f"residual rows rounded [{a[0].shape[0]} rows]", el(a[0]) + a[0].numel() * 2, 0.0
+        if name == "token_gate":
+            return f"side embedding's gate [{a[0].shape[0]} rows of {a[0].shape[1]}]", el(a[0]) + a[0].numel() * 4, 0.0
+        if name == "embed_pairs":
+            T, E = a[0].n_tokens, a[1].shape[1]
+            return f"embedding + pair embedding [{T} rows]", T * E * (2 + 2 + 4), 0.0
         if name == "latent_norm_append":
             down, qr, kr = a[0], a[1], a[2]
             T = down.shape[0]
@@ -739,7 +792,7 @@ def main():
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="run one of the other generation workloads end to end instead (one short line)")
     ap.add_argument("--design", default=None, choices=sorted(DESIGN_SIZES),
-                    help="instead of the headline: prefill and decode of another design (Safuvik; vaderax_*: Vaderax) beside the Llama decoder of "
+                    help="instead of the headline: prefill and decode of another design (Safuvik; vaderax_*: Vaderax; nifarax_*; gozotar_*: Gozotar beside Nifarax) beside the Llama decoder of "
                          "equal size at these layer sizes, nifarax_*: Nifarax beside Vaderax (uses --batch, --context, --prefill-tokens, "
                          "--steps)")
     args = ap.parse_args()

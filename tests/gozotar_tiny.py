@@ -74,12 +74,12 @@ CFG_B = model(64, 80, [
 #: no side embedding; sizes the tensor-core kernels take (heads of 64, widths and inner sizes that are multiples of 16);
 #: three layers that mix values around one that does not; four taps
 CFG_C = model(128, 128, [
-    attention_layer(4, 1, 64, 32, 0.125, rot(250000.0, 32, (4.0, 1.0, 4.0, 32)), 30.0, True, ff=64),
-    latent_layer(4, 32, 16, 32, 48, 0.14, base=1000000.0, ff=64),
+    attention_layer(4, 2, 64, 48, 0.11, rot(200000.0, 32, (6.0, 1.0, 3.0, 32)), 20.0, True, ff=64),
+    latent_layer(4, 32, 16, 32, 48, 0.14, base=50000.0, ff=64),
     attention_layer(2, 2, 64, 64, 0.1, rot(1000.0, 64), None, False, ff=None),
-    attention_layer(4, 1, 64, 32, 0.125, rot(250000.0, 32), 30.0, True, ff=64),
-    parallel_layer((4, 2, 64, 0.19, 4, rot(500000.0, 32)), (2, 32, 32, [0.96875, 0.998], rot(1000000.0, 32)), 0.6, 0.5, ff=64),
-    attention_layer(4, 1, 64, 32, 0.11, rot(10000.0, 16), None, True, ff=None)], bigram=(1021, 127, 7))
+    attention_layer(4, 2, 64, 48, 0.13, rot(200000.0, 32), 25.0, True, ff=64),
+    parallel_layer((4, 2, 64, 0.2, 4, rot(300000.0, 32)), (2, 32, 48, [0.95, 0.995], rot(70000.0, 32)), 0.8, 0.3, ff=64),
+    attention_layer(4, 2, 64, 48, 0.1, rot(10000.0, 16), None, True, ff=None)], bigram=(509, 31, 5))
 
 #: one layer of each kind, every product on the plain path (odd widths), a latent smaller than a head
 CFG_D = model(50, 36, [

@@ -18,7 +18,10 @@ pytestmark = pytest.mark.gpu
 # rounding.  bfloat16: operands of the products, q, the cache, the attention's P and the rows between a feed-forward's
 # products are rounded to 8 bits.
 TOL = {"float32": 2e-4, "bfloat16": 6e-2}
-BAND = {"float32": cases.Band(2e-4), "bfloat16": cases.Band(6e-2, spread=4.0)}
+# whole models in bfloat16, matrices spread by 4: a retention head's outputs are divided by their root mean square, which
+# at a sequence's first positions is |k . q| |v| of one or two tokens and can be as small as its own rounding; such
+# single positions may lie outside the band (one in twenty), while the median stays within a third of it
+BAND = {"float32": cases.Band(2e-4), "bfloat16": cases.Band(6e-2, spikes=0.05, spread=4.0)}
 DTYPES = ["float32", "bfloat16"]
 
 
@@ -210,8 +213,8 @@ def _attention_case(kind, H, G, D, Dv, E, g):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("kind,H,G,D,Dv", [("left", 4, 2, 16, 16), ("left", 6, 2, 64, 64), ("left", 3, 3, 24, 24),
-                                           ("capped", 4, 2, 16, 8), ("capped", 8, 1, 64, 32), ("capped", 2, 2, 40, 56),
+@pytest.mark.parametrize("kind,H,G,D,Dv", [("left", 4, 2, 16, 16), ("left", 8, 4, 64, 64), ("left", 3, 3, 24, 24),
+                                           ("capped", 4, 2, 16, 8), ("capped", 8, 2, 64, 48), ("capped", 2, 2, 40, 56),
                                            ("whole", 4, 4, 128, 128), ("capped", 16, 2, 8, 8)])
 def test_prepared_attention_part(dtype, kind, H, G, D, Dv):
     """Grouped attention behind the kernel that prepares q, k and v, over the paged cache: whole, in portions across a
@@ -300,7 +303,7 @@ def test_retention_part(H, D, Dv, dims, chunks):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,D,R,Dv,C", [(4, 16, 8, 8, 24), (2, 24, 4, 40, 12), (8, 64, 16, 64, 96), (4, 32, 32, 32, 96),
+@pytest.mark.parametrize("H,D,R,Dv,C", [(4, 16, 8, 8, 24), (2, 24, 4, 40, 12), (8, 64, 16, 64, 80), (4, 32, 32, 32, 96),
                                         (1, 8, 2, 8, 200), (2, 64, 64, 16, 64), (16, 16, 16, 32, 240)])
 def test_latent_attention_with_a_turned_key_part(dtype, H, D, R, Dv, C):
     """Attention through latents with a shared turned key part and sinks, over the paged cache: whole, in portions
