@@ -145,6 +145,9 @@ class Model:
     def forward(self, ctx) -> Optional[torch.Tensor]:
         """Runs the step's tokens; returns float32 logits [wanted rows, vocab] or None."""
         ops, meta = ctx.ops, ctx.meta
+        # what parts share within ONE pass over the layers (the values a first layer leaves for later ones, say); a
+        # step's meta may serve several passes (the trial run and the capture of a decode step), this dict serves one
+        ctx.pass_state = {}
         if self.embedding_pairs is None:
             x = ops.embed(meta.token_ids, self.embedding, self.embedding_scale)   # float32 residual stream [T, E]
         else:

@@ -178,9 +178,10 @@ class Attention(Mixer):
         mix = None
         if self.value_mix:
             v_at = (H + Kh) * D
-            first = ctx.meta.extra.get("value_mix_first")
+            shared = ctx.pass_state                      # lives for one pass over the layers (see engine/model.py)
+            first = shared.get("value_mix_first")
             if first is None:
-                ctx.meta.extra["value_mix_first"] = (proj, v_at, Kh * Dv)     # this step's first such layer
+                shared["value_mix_first"] = (proj, v_at, Kh * Dv)             # this pass's first such layer
             else:
                 if first[2] != Kh * Dv:
                     raise ValueError("attention: layers that mix values have values of one size")

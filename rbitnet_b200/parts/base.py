@@ -98,7 +98,8 @@ class Mixer(Part):
     def forward(self, ctx, h: torch.Tensor, entry: int, accumulate_into: Optional[torch.Tensor] = None):
         """h[T, E]: the normed input rows of this step's tokens.  ``entry`` is the
         index of this run in the schedule (``ctx.cache_view(entry)``,
-        ``ctx.state_view(entry)``).  The result is added to ``accumulate_into``; a mixer that
+        ``ctx.state_view(entry)``); ``ctx.pass_state`` is a dict that lives for one pass over the layers, for what
+        a layer leaves for later layers of the same pass.  The result is added to ``accumulate_into``; a mixer that
         can also stand beside another one returns it as float32 [T, E] when that is None."""
         raise NotImplementedError
 

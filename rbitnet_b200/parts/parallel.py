@@ -26,6 +26,10 @@ class _BranchContext:
     def cache_view(self, entry):
         return self._ctx.cache_view(entry)
 
+    @property
+    def pass_state(self):
+        return self._ctx.pass_state
+
     def state_view(self, entry):
         whole = self._ctx.state_view(entry) or {}
         mine = {k[len(self._prefix):]: v for k, v in whole.items() if k.startswith(self._prefix)}

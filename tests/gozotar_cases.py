@@ -154,7 +154,7 @@ def one_far_key_stands_out(make_engine, kind, tol, n, far, cuts, last_only=False
     V = cfg["vocab"]
     toks = [1 + (i * 7) % (V - 3) for i in range(n)]
     toks[far] = V - 1
-    toks[-1] = V - 1 if kind == "latent" else V - 2
+    toks[-1] = V - 2
     noise = torch.randn(cfg["width"], generator=torch.Generator().manual_seed(7)) * float(tensors["embed"][V - 1].std())
     tensors["embed"][V - 2] = tensors["embed"][V - 1] + 0.3 * noise
     m = cfg["layers"][0]["mixer"]
@@ -167,7 +167,12 @@ def one_far_key_stands_out(make_engine, kind, tol, n, far, cuts, last_only=False
         q[:, D:] *= 0.05
         tensors["l0.mix.q"] = q.reshape(H * (D + R), -1)
         tensors["l0.mix.dkv"][C:] *= 0.05
-        m["scale"] = 3.0
+        tensors["l0.mix.sink"] = torch.full_like(tensors["l0.mix.sink"], -4.0)
+        # sharp: the far key's score is 30, the others' a fraction of it
+        x_far = tensors["embed"][V - 1].double()
+        c_far = plain.rms((dkv[:C].double() @ x_far)[None], cfg["norm"]["eps"])[0] * tensors["l0.mix.dkv.norm"].double()
+        match = ((q[:, :D].double() @ x_far) * (uk.double() @ c_far).view(H, D)).sum(-1)
+        m["scale"] = 30.0 / float(match.min())
     elif kind == "attention":
         H, G, D = m["heads"], m["kv_heads"], m["dim"]
         k = tensors["l0.mix.k"].view(G, D, -1).clone()

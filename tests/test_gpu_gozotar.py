@@ -137,6 +137,7 @@ def _meta(ops, runs, tokens=None):
 class _Ctx:
     def __init__(self, ops, meta=None, state=None, cache=None):
         self.ops, self.meta, self._state, self._cache = ops, meta, state, cache
+        self.pass_state = {}
 
     def state_view(self, entry):
         return self._state
@@ -146,7 +147,7 @@ class _Ctx:
 
 
 def _random_weights(part, g, scale=0.3):
-    return {k: (torch.randn(*shape, generator=g) * (scale if len(shape) > 1 else 1.0)).to(torch.bfloat16).double()
+    return {k: (torch.randn(tuple(shape), generator=g) * (scale if len(shape) > 1 else 1.0)).to(torch.bfloat16).double()
             for k, (shape, _) in part.weight_shapes().items()}
 
 
@@ -254,10 +255,10 @@ def test_prepared_attention_part(dtype, kind, H, G, D, Dv):
                 cache.reserve(s, hi - lo)
             cache.upload_tables()
             meta = _meta(ops, [(slots[1], lo, hi - lo), (slots[2], lo, hi - lo)])
+            ctx = _Ctx(ops, meta, state=state, cache=cache)
             if kind != "left":
                 rows = torch.cat([first[lo:hi], first[T + lo:T + hi]]).contiguous()
-                meta.extra["value_mix_first"] = (rows, 5, G * Dv)
-            ctx = _Ctx(ops, meta, state=state, cache=cache)
+                ctx.pass_state["value_mix_first"] = (rows, 5, G * Dv)
             out = part.forward(ctx, torch.cat([ha[lo:hi], hb[lo:hi]]).to(dtype).cuda(), 0)
             outs[0].append(out[:hi - lo])
             outs[1].append(out[hi - lo:])
@@ -322,7 +323,7 @@ def test_latent_attention_with_a_turned_key_part(dtype, H, D, R, Dv, C):
     h = torch.randn(T, E, generator=g).to(torch.bfloat16).double()
     m = {"heads": H, "dim": D, "rot_dim": R, "vdim": Dv, "kv_rank": C, "scale": 0.3, "rot": {"base": 50.0, "dims": R}}
     want = plain.latent_attention(h, m, w, 1e-5)
-    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    tol = 2e-5 if dtype == torch.float32 else 4e-2
     for cuts in ([0, T], [0, 1, 2, 63, 64, 66, T], list(range(T + 1))):
         cache = SequenceCache({0: part.cache_need()}, {}, {}, 64 * 4, 256, dtype, ops.device)
         cache.alloc()
