@@ -582,10 +582,11 @@ DESIGN_SIZES = {
                       _vaderax_shape(2048, 16, 4, 128, 16, 8, 128, 128, 5632, 30, 4, 1408, 4)),
     "nifarax_w4096": (_nifarax_shape(4096, 16, 128, 256, 32, 128, 1536, 256, 64, 8, 1792, 1792, 3),
                       _vaderax_shape(4096, 32, 8, 128, 32, 16, 128, 128, 14336, 62, 8, 1792, 3)),
-    # Gozotar beside Nifarax (attention through latents and a matrix memory with decays both): 6 layers beside 6 runs, 3 beside 3
-    "gozotar_w2048": (_gozotar_shape(2048, 16, 4, 128, 128, 16, 128, 64, 512, 8, 128, 256, 5632, 6),
+    # Gozotar beside Nifarax (attention through latents and a matrix memory with decays both): 6 layers beside 6 runs, 3
+    # beside 3; the cached rows of the latent layers (latent + turned key part) are as wide as Nifarax's latents, 128 and 256
+    "gozotar_w2048": (_gozotar_shape(2048, 16, 4, 128, 128, 16, 128, 32, 96, 8, 128, 256, 5632, 6),
                       _nifarax_shape(2048, 8, 128, 256, 16, 128, 768, 128, 32, 4, 1408, 1408, 6)),
-    "gozotar_w4096": (_gozotar_shape(4096, 32, 8, 128, 128, 32, 128, 64, 512, 16, 128, 256, 14336, 3),
+    "gozotar_w4096": (_gozotar_shape(4096, 32, 8, 128, 128, 32, 128, 64, 192, 16, 128, 256, 14336, 3),
                       _nifarax_shape(4096, 16, 128, 256, 32, 128, 1536, 256, 64, 8, 1792, 1792, 3)),
 }
 

@@ -52,6 +52,9 @@ struct Params {
   int H, G;
   float scale_log2;         // scale * log2(e)
   int window;               // 0: none
+  const float* sinks;       // [H] or null: a term exp(sinks[h]) in head h's denominator
+  float softcap;            // > 0: score <- softcap * tanh(score * scale / softcap)
+  float scale;
   float* part_o;            // [B, H, n_splits, D]
   float* part_ml;           // [B, H, n_splits, 2]
   int n_splits;
@@ -163,6 +166,17 @@ __global__ void __launch_bounds__(WARPS_D * 32) attn_decode_tma_kernel(const __g
   for (int i = 0; i < DT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const bool row_ok[2] = {g < G, g + 8 < G};
+  if (p.sinks != nullptr && warp == 0 && blockIdx.z == 0) {
+    // the sink counts once per row: in the sums of one thread of the row's quad, of one warp, of one part
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (row_ok[h]) {
+        m_run[h] = p.sinks[kvh * G + g + 8 * h] * 1.4426950408889634f;
+        l_run[h] = t4 == 0 ? 1.f : 0.f;
+      }
+    }
+  }
+  const float cap_log2 = p.softcap * 1.4426950408889634f, scale_over_cap = p.softcap > 0.f ? p.scale / p.softcap : 0.f;
   const uint32_t q_base = smem_u32(sQ);
   bool failed = false;
   __syncthreads();                       // Q is in shared memory
@@ -199,7 +213,8 @@ __global__ void __launch_bounds__(WARPS_D * 32) attn_decode_tma_kernel(const __g
           const int h = c >> 1;
           const int key = key_base + n * 8 + t4 * 2 + (c & 1);
           const bool ok = row_ok[h] && key <= pos0 && key >= key_lo;
-          const float v = ok ? (s[n][c] + s2[n][c]) * p.scale_log2 : -INFINITY;
+          const float sc = s[n][c] + s2[n][c];
+          const float v = !ok ? -INFINITY : (p.softcap > 0.f ? cap_log2 * tanhf(sc * scale_over_cap) : sc * p.scale_log2);
           s[n][c] = v;
           m_new[h] = fmaxf(m_new[h], v);
         }

@@ -102,8 +102,7 @@ RbAttentionOptions rb_attention_take() {
   return o;
 }
 
-// For the calling thread's next attention launch (any of the library's attention entry points that takes them:
-// rb_attention_simple, rb_attention_prefill, rb_attention_decode); see rb_common.cuh.
+// For the calling thread's next attention launch (any of the library's attention entry points); see rb_common.cuh.
 RB_EXPORT int rb_attention_next(const float* sinks, float softcap) {
   t_next_attention.sinks = sinks;
   t_next_attention.softcap = softcap > 0.f ? softcap : 0.f;

@@ -47,6 +47,9 @@ struct TcAttnParams {
   int H, G;
   float scale_log2;
   int window;
+  const float* sinks;       // [H] or null: a term exp(sinks[h]) in head h's denominator
+  float softcap;            // > 0: score <- softcap * tanh(score * scale / softcap), before the mask
+  float scale;
 };
 
 // 2^x for x <= 0 (and -inf -> 0) with the hardware approximation (relative error about 2^-22)
@@ -306,6 +309,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     constexpr int HK = TILE_KEYS / 2;                        // keys per thread and tile
     constexpr int HD = D / 2;                                // columns of O per thread
     float m_run = -INFINITY, l_run = 0.f;
+    if (p.sinks != nullptr && row_ok) {
+      // the sink: one more term of the row's denominator, counted by one of the row's two threads; both start from
+      // the same reference, so that their exponents agree
+      m_run = p.sinks[kvh * G + r % G] * 1.4426950408889634f;
+      l_run = half == 0 ? 1.f : 0.f;
+    }
+    // with a soft cap the values of S become (cap / scale) tanh(S scale / cap), so that everything after this
+    // (the maxima, the scale folded into the exponent) stays as it is; tanh(x) = 1 - 2 / (1 + e^(2x)) with the
+    // hardware's exponential and reciprocal (relative error about 2^-21)
+    const float cap_a = p.softcap > 0.f ? 2.0f * 1.4426950408889634f * p.scale / p.softcap : 0.f;
+    const float cap_b = p.softcap > 0.f ? p.softcap / p.scale : 0.f;
     bool failed = false;
     for (int kt = kt_begin, j = 0; kt < kt_end; ++kt, ++j) {
       bool ok = !failed;
@@ -318,6 +332,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 #pragma unroll
       for (int c = 0; c < HK; c += 16) tmem_ld16(s_addr + c, reinterpret_cast<uint32_t*>(sv + c));
       tmem_ld_wait();
+      if (p.softcap > 0.f) {
+#pragma unroll
+        for (int c = 0; c < HK; ++c) {
+          float e, rc;
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(fminf(sv[c] * cap_a, 126.0f)));
+          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(1.0f + e));
+          sv[c] = fmaf(-2.0f * cap_b, rc, cap_b);
+        }
+      }
       const int key_base = kt * TILE_KEYS + half * HK;
       // a tile that every row of the CTA sees whole needs no mask (all tiles but those on the
       // diagonal and at the window's edge)
@@ -538,6 +561,7 @@ RB_EXPORT int rb_attention_decode_tma(void* out, const void* q, const void* cach
   p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size; p.n_kv_heads = Kh;
   p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.H = H; p.G = H / Kh;
   p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+  { const RbAttentionOptions opt = rb_attention_take(); p.sinks = opt.sinks; p.softcap = opt.softcap; p.scale = scale; }
   p.part_o = part_o; p.part_ml = part_ml; p.n_splits = n_splits; p.cluster = cluster ? 1 : 0;
   const int rc = D == 64 ? decode_tma::launch<64>(tk, tv, p, B, Kh, stream) : decode_tma::launch<128>(tk, tv, p, B, Kh, stream);
   if (rc != 0) return rc;
@@ -575,6 +599,7 @@ RB_EXPORT int rb_attention_prefill_tc(void* out, const void* q, const void* cach
   p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size; p.n_kv_heads = Kh;
   p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.tile_tok0 = tile_tok0; p.tile_ntok = tile_ntok; p.n_tiles = n_tiles;
   p.H = H; p.G = H / Kh; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+  { const RbAttentionOptions opt = rb_attention_take(); p.sinks = opt.sinks; p.softcap = opt.softcap; p.scale = scale; }
   if (D == 64) return launch_tc<64>(tk, tv, p, Kh, stream);
   return launch_tc<128>(tk, tv, p, Kh, stream);
 }

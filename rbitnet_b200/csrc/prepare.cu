@@ -43,6 +43,17 @@ __device__ __forceinline__ float turned(F val, int e, int rot_dim, int interleav
   return first ? me * cs - ot * sn : me * cs + ot * sn;
 }
 
+// one or two neighbouring values (two: the address is a multiple of two values)
+template <typename T> __device__ __forceinline__ void rb_store_values(T* dst, const float* y, int n);
+template <> __device__ __forceinline__ void rb_store_values<float>(float* dst, const float* y, int n) {
+  if (n == 2) *reinterpret_cast<float2*>(dst) = make_float2(y[0], y[1]);
+  else dst[0] = y[0];
+}
+template <> __device__ __forceinline__ void rb_store_values<__nv_bfloat16>(__nv_bfloat16* dst, const float* y, int n) {
+  if (n == 2) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(y[0], y[1]);
+  else dst[0] = __float2bfloat16_rn(y[0]);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) round_rows_kernel(T* __restrict__ out, const float* __restrict__ x, int64_t n) {
   rb_pdl_launch_dependents();
@@ -180,19 +191,18 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(T* __restrict__ q_out, 
   rb_pdl_wait();
   const float* row = p.proj + (int64_t)t * p.ld;
   if (p.conv_w != nullptr) {
+    // tap by tap over all channels, so that a thread's loads of one pass do not wait for one another
     const int K = p.K;
     const int pos0 = p.tok_first != nullptr ? p.tok_pos[p.tok_first[t]] : pos;     // the run's first position
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-      float acc = 0.f;
-      for (int j = 0; j < K; ++j) {
-        const int back = K - 1 - j, at = pos - back;
-        if (at < 0) continue;
-        const float u = at >= pos0 ? row[c - (int64_t)back * p.ld] : p.tail[((int64_t)slot * K + at % K) * C + c];
-        acc = fmaf(p.conv_w[(int64_t)c * K + j], u, acc);
-      }
-      s_qk[c] = acc;
-      if (p.tok_first == nullptr && K > 1) p.tail[((int64_t)slot * K + pos % K) * C + c] = row[c];   // a row that is its own run
+    for (int c = threadIdx.x; c < C; c += blockDim.x) s_qk[c] = p.conv_w[(int64_t)c * K + K - 1] * row[c];
+    for (int back = 1; back < K && back <= pos; ++back) {
+      const int at = pos - back;
+      const float* src = at >= pos0 ? row - (int64_t)back * p.ld : p.tail + ((int64_t)slot * K + at % K) * C;
+      for (int c = threadIdx.x; c < C; c += blockDim.x)
+        s_qk[c] = fmaf(p.conv_w[(int64_t)c * K + K - 1 - back], src[c], s_qk[c]);
     }
+    if (p.tok_first == nullptr && K > 1)                                           // a row that is its own run
+      for (int c = threadIdx.x; c < C; c += blockDim.x) p.tail[((int64_t)slot * K + pos % K) * C + c] = row[c];
   } else {
     for (int c = threadIdx.x; c < C; c += blockDim.x) s_qk[c] = row[c];
   }
@@ -219,18 +229,25 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(T* __restrict__ q_out, 
   __syncthreads();
   T* kdst = (T*)cache.k;
   T* vdst = (T*)cache.v;
-  for (int idx = threadIdx.x; idx < (H + Kh) * Dc; idx += blockDim.x) {
-    const int head = idx / Dc, e = idx - head * Dc;
+  // a thread makes `step` neighbouring values of a head at a time (two where the cache rows have an even width)
+  const int step = (Dc & 1) ? 1 : 2;
+  for (int idx = threadIdx.x * step; idx < (H + Kh) * Dc; idx += blockDim.x * step) {
+    const int head = idx / Dc, e0 = idx - head * Dc;
     const bool is_q = head < H;
     T* dst = is_q ? q_out + ((int64_t)t * H + head) * Dc : kdst + rb_page_offset(cache, slot, pos, head - H);
-    if (e >= D) { dst[e] = rb_from_float<T>(0.f); continue; }
     const float* src = s_qk + head * D;
     const float* nw = is_q ? p.q_norm_w : p.k_norm_w;
     const int wbase = p.norm_mode == 1 ? (is_q ? head : head - H) * D : 0;
     const float fac = p.norm_mode ? s_fac[head] : 1.f;
     const int mode = p.norm_mode;
     auto val = [&](int i) { return mode ? src[i] * fac * nw[wbase + i] : src[i]; };
-    dst[e] = rb_from_float<T>(turned(val, e, p.rot_dim, p.interleaved, s_sincos));
+    float y[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int e = e0 + k;
+      y[k] = (k < step && e < D) ? turned(val, e, p.rot_dim, p.interleaved, s_sincos) : 0.f;
+    }
+    rb_store_values<T>(dst + e0, y, step);
   }
   const int v_at = C;                                        // own values follow the keys in a row
   for (int idx = threadIdx.x; idx < Kh * Dc; idx += blockDim.x) {

@@ -454,21 +454,18 @@ class CudaOps:
                   window: Optional[int], sinks: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
         """Each new token's queries over its sequence's cached keys up to its own position.  ``sinks`` (float32 [H]):
         head h's softmax denominator also holds exp(sinks[h]); ``softcap`` > 0: score <- softcap * tanh(score /
-        softcap).  With either, the kernels that know them run: the mma.sync prefill and split decode kernels in
-        bfloat16 (head sizes they take), else the plain kernel."""
+        softcap).  Every attention kernel of the library takes both."""
         T, H, D = q.shape
         Kh = view.n_kv_heads
         out = torch.empty((T, H * D), dtype=self.dtype, device=self.device)
         win = int(window or 0)
-        optioned = sinks is not None or softcap > 0.0
-        if optioned:
+        if sinks is not None or softcap > 0.0:
             if sinks is not None:
                 self._check(sinks, torch.float32, "attention sinks")
             self.lib.call("rb_attention_next", _ptr(sinks), float(softcap), launches=0)
         if self.dtype == torch.bfloat16 and meta.single_token and \
                 self.lib.raw("rb_attention_tiled_supports")(H, Kh, D, view.page_size, 1):
-            on_tma = self.decode_on_tma and not optioned and \
-                self.lib.raw("rb_attention_decode_tma_supports")(H, Kh, D, view.page_size)
+            on_tma = self.decode_on_tma and self.lib.raw("rb_attention_decode_tma_supports")(H, Kh, D, view.page_size)
             if on_tma:
                 n_splits = self.lib.raw("rb_attention_decode_tma_parts")(T * Kh, max(1, -(-meta.max_context // 64)), D)
             else:
@@ -491,7 +488,7 @@ class CudaOps:
                               _ptr(view.page_table), view.max_pages, view.page_size, _ptr(meta.tok_pos),
                               _ptr(meta.tok_slot), T, H, Kh, D, float(scale), win, _ptr(part_o), _ptr(part_ml),
                               n_splits, self._stream(), launches=2 if n_splits > 1 else 1)
-        elif self.dtype == torch.bfloat16 and self.prefill_on_tcgen05 and not optioned and \
+        elif self.dtype == torch.bfloat16 and self.prefill_on_tcgen05 and \
                 self.lib.raw("rb_attention_prefill_tc_supports")(H, Kh, D, view.page_size):
             tok0, ntok, n_tiles = self._prefill_tiles(meta, 128 // (H // Kh))
             self.lib.call("rb_attention_prefill_tc", _ptr(out), _ptr(q), _ptr(view.k), _ptr(view.v),
