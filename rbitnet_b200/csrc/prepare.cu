@@ -58,7 +58,16 @@ template <typename T>
 __global__ void __launch_bounds__(256) round_rows_kernel(T* __restrict__ out, const float* __restrict__ x, int64_t n) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+  // four values a thread and turn where the addresses allow 16-byte loads, the rest value by value
+  const bool vec = ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % (4 * sizeof(T)) == 0);
+  const int64_t n4 = vec ? n / 4 : 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    const float4 v = *reinterpret_cast<const float4*>(x + 4 * i);
+    const float y[4] = {v.x, v.y, v.z, v.w};
+    rb_store_values<T>(out + 4 * i, y, 2);
+    rb_store_values<T>(out + 4 * i + 2, y + 2, 2);
+  }
+  for (int64_t i = 4 * n4 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
     out[i] = rb_from_float<T>(x[i]);
 }
 
@@ -174,7 +183,7 @@ struct QkParams {
 // A block per token.  Shared memory: rot_dim sines and cosines, the C = (H + Kh) D convolved q and k values, a factor
 // per head.
 template <typename T>
-__global__ void __launch_bounds__(256) qk_prepare_kernel(T* __restrict__ q_out, T* __restrict__ gates_out, QkParams p,
+__global__ void __launch_bounds__(1024) qk_prepare_kernel(T* __restrict__ q_out, T* __restrict__ gates_out, QkParams p,
                                                          RbPagedLayer cache) {
   rb_pdl_launch_dependents();
   __shared__ float scratch[33];
@@ -229,40 +238,51 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(T* __restrict__ q_out, 
   __syncthreads();
   T* kdst = (T*)cache.k;
   T* vdst = (T*)cache.v;
-  // a thread makes `step` neighbouring values of a head at a time (two where the cache rows have an even width)
+  // a warp takes a head at a time (no division per value); a lane makes `step` neighbouring values of it at a time
+  // (two where the cache rows have an even width)
   const int step = (Dc & 1) ? 1 : 2;
-  for (int idx = threadIdx.x * step; idx < (H + Kh) * Dc; idx += blockDim.x * step) {
-    const int head = idx / Dc, e0 = idx - head * Dc;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const int mode = p.norm_mode;
+  for (int head = warp; head < H + Kh; head += n_warps) {
     const bool is_q = head < H;
     T* dst = is_q ? q_out + ((int64_t)t * H + head) * Dc : kdst + rb_page_offset(cache, slot, pos, head - H);
     const float* src = s_qk + head * D;
-    const float* nw = is_q ? p.q_norm_w : p.k_norm_w;
-    const int wbase = p.norm_mode == 1 ? (is_q ? head : head - H) * D : 0;
-    const float fac = p.norm_mode ? s_fac[head] : 1.f;
-    const int mode = p.norm_mode;
-    auto val = [&](int i) { return mode ? src[i] * fac * nw[wbase + i] : src[i]; };
-    float y[2];
+    const float* nw = (is_q ? p.q_norm_w : p.k_norm_w) + (mode == 1 ? (is_q ? head : head - H) * D : 0);
+    const float fac = mode ? s_fac[head] : 1.f;
+    auto val = [&](int i) { return mode ? src[i] * fac * nw[i] : src[i]; };
+    for (int e0 = lane * step; e0 < Dc; e0 += 32 * step) {
+      float y[2];
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const int e = e0 + k;
-      y[k] = (k < step && e < D) ? turned(val, e, p.rot_dim, p.interleaved, s_sincos) : 0.f;
+      for (int k = 0; k < 2; ++k) {
+        const int e = e0 + k;
+        y[k] = (k < step && e < D) ? turned(val, e, p.rot_dim, p.interleaved, s_sincos) : 0.f;
+      }
+      rb_store_values<T>(dst + e0, y, step);
     }
-    rb_store_values<T>(dst + e0, y, step);
   }
   const int v_at = C;                                        // own values follow the keys in a row
-  for (int idx = threadIdx.x; idx < Kh * Dc; idx += blockDim.x) {
-    const int kvh = idx / Dc, e = idx - kvh * Dc;
-    float v = 0.f;
-    if (e < Dv) {
-      if (p.values_are_keys) {
-        v = s_qk[(H + kvh) * D + e];
-      } else {
-        v = row[v_at + kvh * Dv + e];
-        if (p.mix_rows != nullptr)
-          v = (1.0f - p.mix_weight) * v + p.mix_weight * p.mix_rows[(int64_t)t * p.mix_ld + kvh * Dv + e];
+  for (int kvh = warp; kvh < Kh; kvh += n_warps) {
+    T* dst = vdst + rb_page_offset(cache, slot, pos, kvh);
+    const float* own = row + v_at + kvh * Dv;
+    const float* other = p.mix_rows != nullptr ? p.mix_rows + (int64_t)t * p.mix_ld + kvh * Dv : nullptr;
+    for (int e0 = lane * step; e0 < Dc; e0 += 32 * step) {
+      float y[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int e = e0 + k;
+        float v = 0.f;
+        if (k < step && e < Dv) {
+          if (p.values_are_keys) {
+            v = s_qk[(H + kvh) * D + e];
+          } else {
+            v = own[e];
+            if (other != nullptr) v = (1.0f - p.mix_weight) * v + p.mix_weight * other[e];
+          }
+        }
+        y[k] = v;
       }
+      rb_store_values<T>(dst + e0, y, step);
     }
-    vdst[rb_page_offset(cache, slot, pos, kvh) + e] = rb_from_float<T>(v);
   }
   if (p.gate_heads) {
     const int g_at = C + (p.values_are_keys ? 0 : Kh * Dv);
@@ -352,9 +372,9 @@ inline int blocks_for(int64_t n, int threads) {
 RB_EXPORT int rb_round_rows(void* out, int out_dtype, const float* x, int64_t n, cudaStream_t stream) {
   if (n == 0) return 0;
   if (out_dtype == RB_BF16)
-    RB_LAUNCH("round_rows_kernel", (round_rows_kernel<__nv_bfloat16>), blocks_for(n, 256), 256, 0, stream, (__nv_bfloat16*)out, x, n);
+    RB_LAUNCH("round_rows_kernel", (round_rows_kernel<__nv_bfloat16>), blocks_for((n + 3) / 4, 256), 256, 0, stream, (__nv_bfloat16*)out, x, n);
   else if (out_dtype == RB_F32)
-    RB_LAUNCH("round_rows_kernel", (round_rows_kernel<float>), blocks_for(n, 256), 256, 0, stream, (float*)out, x, n);
+    RB_LAUNCH("round_rows_kernel", (round_rows_kernel<float>), blocks_for((n + 3) / 4, 256), 256, 0, stream, (float*)out, x, n);
   else
     RB_FAIL("rb_round_rows: unknown dtype %d", out_dtype);
   RB_CHECK_LAUNCH("rb_round_rows");
@@ -440,12 +460,19 @@ RB_EXPORT int rb_qk_prepare(void* q_out, void* gates_out, int dtype, const float
              tok_pos, tok_slot, H, D, Dv, values_are_keys, mix_rows, mix_ld, mix_weight, gate_heads};
   RbPagedLayer c{cache_k, cache_v, page_table, max_pages, page_size, Kh, Dc};
   const size_t smem = ((size_t)rot_dim + (size_t)(H + Kh) * D + (size_t)(H + Kh)) * sizeof(float);
+  // few tokens (a decode step): a token's block is the whole chain, so it gets as many threads as it has pairs of
+  // values to make; many tokens: blocks of 256, several of which share an SM
+  int threads = 256;
+  if (T <= 2 * rb_sm_count()) {
+    const int pairs = (H + Kh) * Dc / 2;
+    threads = pairs >= 1024 ? 1024 : (pairs >= 512 ? 512 : 256);
+  }
   RB_REQUIRE(smem <= 200 * 1024, "rb_qk_prepare: %d q and k values per token do not fit shared memory", (H + Kh) * D);
 #define GO(TT)                                                                                                          \
   do {                                                                                                                  \
     if (smem > 48 * 1024)                                                                                               \
       RB_CUDA(cudaFuncSetAttribute(qk_prepare_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
-    RB_LAUNCH("qk_prepare_kernel", (qk_prepare_kernel<TT>), T, 256, smem, stream, (TT*)q_out, (TT*)gates_out, p, c);    \
+    RB_LAUNCH("qk_prepare_kernel", (qk_prepare_kernel<TT>), T, threads, smem, stream, (TT*)q_out, (TT*)gates_out, p, c); \
   } while (0)
   if (dtype == RB_BF16) GO(__nv_bfloat16);
   else if (dtype == RB_F32) GO(float);
