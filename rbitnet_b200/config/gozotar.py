@@ -68,8 +68,8 @@ class GozotarConfig(ModelConfig):
             for k in ("mul_prev", "mul_cur"):
                 if not isinstance(bigram[k], int) or isinstance(bigram[k], bool) or bigram[k] < 0:
                     raise ConfigError(f"config.json: embedding.bigram.{k} must be a whole number, not negative")
-            if (self.vocab - 1) * (bigram["mul_prev"] + bigram["mul_cur"]) >= 2 ** 31:
-                raise ConfigError("config.json: embedding.bigram: the pair's sum does not fit 31 bits")
+            if max(bigram["buckets"], bigram["mul_prev"], bigram["mul_cur"]) >= 2 ** 31:
+                raise ConfigError("config.json: embedding.bigram: buckets and multipliers must fit 31 bits")
         if self.token_side:
             _need(self.token_side, ("dim",), "token_side")
             _positive_int(self.token_side["dim"], "token_side.dim")

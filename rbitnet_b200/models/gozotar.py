@@ -82,6 +82,10 @@ def build_gozotar_spec(cfg: GozotarConfig) -> ModelSpec:
             names.update({"ffn_norm.weight": f"l{i}.norm2", "ffn_norm.scale": f"l{i}.ls2"})
         else:
             ignorable += [f"l{i}.norm2", f"l{i}.ls2"]
+        if layer["type"] == "attention" and not layer["mixer"].get("v_mix"):
+            ignorable.append(f"l{i}.mix.vmix")                   # a layer that mixes nothing may still carry the number
+        if not cfg.token_side:
+            ignorable.append(f"l{i}.side.*")
         if cfg.token_side:
             parts["token_input"] = PartSpec("gated_embedding", {
                 "width": cfg.width, "dim": int(cfg.token_side["dim"]), "vocab": cfg.vocab, "index": i, "n_slices": n_layers,
@@ -94,6 +98,10 @@ def build_gozotar_spec(cfg: GozotarConfig) -> ModelSpec:
                     names[f"{part_name}.{key}"] = f"l{i}.{prefix}.{key}"
         layers.append(BlockSpec(parts=parts, names=names, arrangement="post_norm"))
     bigram = (cfg.embedding or {}).get("bigram")
+    if not bigram:
+        ignorable.append("bigram")
+    if not cfg.token_side:
+        ignorable.append("side.embed")
     return ModelSpec(
         width=cfg.width, vocab_size=cfg.vocab, embedding_name="embed", layers=layers,
         schedule=[ScheduleEntry(i) for i in range(n_layers)],

@@ -27,7 +27,7 @@ kernel (``ops.qk_prepare``) does everything between it and the attention:
                    multiplied by a weight of the head's size that all heads share ("q.norm", "k.norm")
   conv_taps        a short causal convolution over time on every channel of the q and k projections ("q.conv",
                    "k.conv": [channels, taps], the last tap is the current row's), directly after the product; the
-                   last taps - 1 projected rows of a sequence are its state
+                   last taps - 1 projected rows of a sequence are its state (one tap only scales the channels)
   values           "keys": there is no value matrix; a position's values are its keys as they leave the convolution,
                    before norm and rotation
   softcap          score <- softcap * tanh(score / softcap) before the softmax
@@ -73,7 +73,7 @@ class Attention(Mixer):
         if self.values_are_keys and value_mix:
             raise ValueError("attention: values that are the keys are not mixed with another layer's")
         #: the options of the module's third paragraph: float32 projections and one kernel before the attention
-        self.prepared = bool(self.conv_taps > 1 or self.values_are_keys or self.softcap or self.value_mix or self.sinks
+        self.prepared = bool(self.conv_taps >= 1 or self.values_are_keys or self.softcap or self.value_mix or self.sinks
                              or qk_norm == "head_weight")
         if self.prepared and (qk_norm == "head" or value_gate):
             raise ValueError("attention: a weightless norm per head after the rotation and a gate per value do not go "
@@ -105,7 +105,7 @@ class Attention(Mixer):
             shapes["k.norm"] = ((D,), "norm")
         if self.values_are_keys:
             del shapes["v"]
-        if self.conv_taps > 1:
+        if self.conv_taps >= 1:
             shapes["q.conv"] = ((H * D, self.conv_taps), "taps")
             shapes["k.conv"] = ((K * D, self.conv_taps), "taps")
         if self.value_mix:
@@ -138,7 +138,7 @@ class Attention(Mixer):
             if self.qk_norm:
                 self.q_norm_w = weights["q.norm"].to(**f32).contiguous()
                 self.k_norm_w = weights["k.norm"].to(**f32).contiguous()
-            if self.conv_taps > 1:
+            if self.conv_taps >= 1:
                 self.conv_w = torch.cat([weights["q.conv"], weights["k.conv"]], dim=0).to(**f32).contiguous()
             if self.value_mix:
                 self.mix_weight = float(weights["vmix"].to(torch.float32).reshape(-1)[0])

@@ -130,6 +130,30 @@ def test_value_mixing_takes_the_first_such_layer():
     assert cases.rel_err(cases.run_cut(eng, toks, [7]), plain.forward(cfg, other, toks)) <= TOL
 
 
+def test_one_tap_and_tensors_a_model_does_not_use(tmp_path):
+    """A convolution of one tap only scales the channels and keeps no ring; a folder may hold a mixing weight for a
+    layer that mixes nothing, norms of a feed-forward that a layer does not have, and embeddings the configuration
+    does not ask for."""
+    from gozotar_tiny import model, parallel_layer, attention_layer, rot
+    cfg = model(40, 32, [parallel_layer((2, 1, 8, 0.3, 1, rot(100.0, 8)), (2, 16, 8, [0.9, 0.99], rot(1000.0, 16)), 0.5, 1.0),
+                         attention_layer(2, 1, 8, 4, 0.3, rot(50.0, 4), None, False, ff=None)])
+    tensors = make_tensors(cfg, 3)
+    assert tensors["l0.mix.left.q.conv"].shape == (16, 1)
+    toks = tokens_for(cfg, 20, 1)
+    eng = make_engine(cfg, tensors)
+    _, _, states = eng.model.cache_plan()
+    assert set(states[0]) == {"right.S"}
+    assert cases.rel_err(cases.run_cut(eng, toks, [5, 6]), plain.forward(cfg, tensors, toks)) <= TOL
+    extra = dict(tensors, **{"l1.mix.vmix": torch.tensor(0.5), "l1.norm2": torch.zeros(32), "l1.ls2": torch.ones(32),
+                             "bigram": torch.zeros(8, 32), "side.embed": torch.zeros(40, 6), "l0.side.gate": torch.zeros(3, 32)})
+    folder = write_model(tmp_path / "m", cfg, extra)
+    eng = Engine.load_path(folder, dtype="float32", ops=TorchOps(torch.float32), max_tokens=256, verbose=False)
+    assert cases.rel_err(cases.run_cut(eng, toks, []), plain.forward(cfg, tensors, toks)) <= TOL
+    with pytest.raises(Exception):
+        Engine.load_path(write_model(tmp_path / "n", cfg, dict(tensors, other=torch.zeros(3))), dtype="float32",
+                         ops=TorchOps(torch.float32), max_tokens=256, verbose=False)
+
+
 def test_state_and_cache_of_a_model():
     eng = make_engine(CONFIGS["A"], make_tensors(CONFIGS["A"], 1))
     caches, _, states = eng.model.cache_plan()

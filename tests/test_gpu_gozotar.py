@@ -117,6 +117,61 @@ def test_captured_step_in_bfloat16():
                                     for i, r in enumerate(reqs)])
 
 
+def test_command_line_and_trace_replay(tmp_path):
+    """``python -m rbitnet_b200 random`` makes a model of the design from its config.json; ``generate --temperature 0``
+    prints the plain model's greedy ids; ``bin/trace_run`` replays a schedule of two unequal requests on the same folder."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    from rbitnet_b200.weights import read_safetensors
+    root = Path(__file__).resolve().parent.parent
+    cfg = CONFIGS["D"]
+    (tmp_path / "cfg.json").write_text(json.dumps(cfg))
+    env = dict(os.environ, PYTHONPATH=str(root))
+    model = tmp_path / "model"
+    p = subprocess.run([sys.executable, "-m", "rbitnet_b200", "random", "--config", str(tmp_path / "cfg.json"), "--out", str(model),
+                        "--seed", "5", "--dtype", "float32"], capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    tensors = {k: v.float() for k, v in read_safetensors(model / "model.safetensors").items()}
+    ps = [tokens_for(cfg, 7, 1), tokens_for(cfg, 3, 2)]
+    cmd = [sys.executable, "-m", "rbitnet_b200", "generate", "--model", str(model), "--dtype", "float32", "--temperature", "0",
+           "--max-tokens", "6", "--cache-tokens", "512"]
+    for q in ps:
+        cmd += ["--prompt-ids", " ".join(map(str, q))]
+    p = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [json.loads(x) for x in p.stdout.strip().splitlines()]
+    assert len(lines) == 2
+    for q, rec in zip(ps, lines):
+        seq = list(q)
+        for tok in rec["tokens"]:
+            logits = plain.forward(cfg, tensors, seq)[-1]
+            best = int(torch.argmax(logits))
+            assert best == tok or float(logits[best] - logits[tok]) <= 1e-4 * float(logits.abs().max())
+            seq.append(tok)
+        assert len(rec["tokens"]) == 6
+    a, b = tokens_for(cfg, 70, 3), tokens_for(cfg, 5, 4)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:66], "want": [0, 64, 65]}, {"id": "b", "tokens": b[:4], "want": [3]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[66:67], "want": [0]}, {"id": "b", "tokens": b[4:], "want": [0]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[67:68], "want": []}], "end": []},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[68:], "want": [0, 1]}], "end": ["a"]}]
+    ra, rb = plain.forward(cfg, tensors, a), plain.forward(cfg, tensors, b)
+    want = {0: torch.stack([ra[0], ra[64], ra[65], rb[3]]), 1: torch.stack([ra[66], rb[4]]), 3: torch.stack([ra[68], ra[69]])}
+    for dtype in DTYPES:
+        out = tmp_path / f"out_{dtype}"
+        p = subprocess.run([str(root / "bin" / "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out),
+                            "--max-tokens", "128"], input="\n".join(json.dumps(x) for x in steps) + "\n", capture_output=True,
+                           text=True, env=env, timeout=600)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert [x for x in p.stdout.split("\n") if x.startswith("done")] == [f"done {i}" for i in range(4)]
+        assert not (out / "2.f32").exists()
+        for step, ref in want.items():
+            got = torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(ref.shape[0], -1).copy())
+            assert rel_err(got, ref) <= (2e-4 if dtype == "float32" else 6e-2), (dtype, step)
+
+
 # ---------------------------------------------------------------- kernels alone
 def _ops(dtype):
     from rbitnet_b200.kernels.ops import CudaOps

@@ -508,7 +508,7 @@ class TorchOps:
                 hist[K - 1:] = x[first:first + n, :C]
                 for i in range(n):
                     qk[first + i] = (hist[i:i + K] * conv.T).sum(0)
-                for i in range(max(0, n - K), n):
+                for i in range(max(0, n - K), n if K > 1 else 0):
                     tail[slot, (p0 + i) % K] = x[first + i, :C]
         q, k = qk[:, :H * D], qk[:, H * D:]
         if values_are_keys:
