@@ -21,6 +21,7 @@ the part's weight key ("q", "dkv.norm", "sink", "vmix", "left.q.conv", "right.g"
 """
 from __future__ import annotations
 
+from ..config.base import ConfigError
 from ..config.registry import register_architecture
 from ..config.gozotar import GozotarConfig
 from ..parts import PartSpec, BlockSpec, ScheduleEntry, ModelSpec, build_part
@@ -69,6 +70,9 @@ _MIXERS = {"latent_attention": _latent, "attention": _attention, "parallel": _pa
 
 
 def build_gozotar_spec(cfg: GozotarConfig) -> ModelSpec:
+    missing = cfg.missing_sizes()
+    if missing:
+        raise ConfigError("config.json: " + ", ".join(missing) + ": neither named nor given by a tensor's shape")
     eps = float(cfg.norm["eps"])
     result_norm = PartSpec("rmsnorm", {"width": cfg.width, "eps": eps, "one_plus": True, "layer_scale": True})
     n_layers = len(cfg.layers)

@@ -154,6 +154,24 @@ def test_one_tap_and_tensors_a_model_does_not_use(tmp_path):
                          ops=TorchOps(torch.float32), max_tokens=256, verbose=False)
 
 
+def test_sizes_that_only_a_tensor_gives(tmp_path):
+    """config.json may leave out the sizes that a tensor's shape gives; what nothing gives is an error."""
+    cfg = CONFIGS["A"]
+    tensors = make_tensors(cfg, 4)
+    bare = json.loads(json.dumps(cfg))
+    bare["layers"][0]["mlp"].pop("ff")
+    bare["layers"][0]["mixer"]["left"].pop("conv")
+    bare["layers"][3]["mixer"].pop("kv_rank")
+    bare["embedding"]["bigram"].pop("buckets")
+    bare["token_side"]["dim"] = None
+    toks = tokens_for(cfg, 12, 2)
+    eng = Engine.load_path(write_model(tmp_path / "m", bare, tensors), dtype="float32", ops=TorchOps(torch.float32),
+                           max_tokens=256, verbose=False)
+    assert cases.rel_err(cases.run_cut(eng, toks, [7]), plain.forward(cfg, tensors, toks)) <= TOL
+    with pytest.raises(ConfigError):
+        spec_of(bare)
+
+
 def test_state_and_cache_of_a_model():
     eng = make_engine(CONFIGS["A"], make_tensors(CONFIGS["A"], 1))
     caches, _, states = eng.model.cache_plan()

@@ -117,6 +117,48 @@ def test_captured_step_in_bfloat16():
                                     for i, r in enumerate(reqs)])
 
 
+def _mid_sizes():
+    """Sizes that every tensor-core kernel takes: cached rows of 128 (tcgen05 prefill, TMA decode) with sinks, heads of
+    128 and of 64 with the soft cap, products of 512 to 2,048 columns."""
+    from gozotar_tiny import model, latent_layer, attention_layer, parallel_layer
+    stretched = (8.0, 1.0, 4.0, 128)
+    return model(1000, 512, [
+        latent_layer(8, 64, 32, 64, 96, 0.1, base=10000.0, ff=1536),
+        attention_layer(8, 2, 128, 64, 0.09, rot(100000.0, 64, stretched), 15.0, True, ff=1536),
+        parallel_layer((8, 2, 64, 0.12, 4, rot(10000.0, 32)), (4, 64, 128, [0.9, 0.97, 0.99, 0.999], rot(5000.0, 64)), 0.7, 0.6,
+                       ff=1536),
+        attention_layer(8, 2, 128, 64, 0.09, rot(100000.0, 64), None, True, ff=1536)], bigram=(4099, 211, 17), side=64)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mid_sizes(dtype):
+    """Whole, the last 40 tokens one by one, and an unequal batch decoded together, at sizes of the tensor-core kernels."""
+    from safuvik_tiny import run_cut
+    from rbitnet_b200.engine.step import StepEntry
+    cfg = _mid_sizes()
+    band = BAND[dtype]
+    tensors = make_tensors(cfg, seed=31, spread=band.spread)
+    eng = engine_maker(dtype)(cfg, tensors, max_tokens=64 * 16)
+    toks = tokens_for(cfg, 200, 9)
+    ref = plain.forward(cfg, tensors, toks)
+    assert band.ok(run_cut(eng, toks, []), ref)
+    assert band.ok(run_cut(eng, toks, list(range(160, 200))), ref)
+    reqs = [toks[:150], tokens_for(cfg, 70, 10), tokens_for(cfg, 9, 11)]
+    refs = [ref[:150]] + [plain.forward(cfg, tensors, r) for r in reqs[1:]]
+    slots = [eng.new_sequence() for _ in reqs]
+    cut = [len(r) - 5 for r in reqs]
+    out = eng.step([StepEntry(s, r[:n], list(range(n))) for s, r, n in zip(slots, reqs, cut)])
+    got, at = [], 0
+    for n in cut:
+        got.append([out[at:at + n]])
+        at += n
+    for k in range(5):
+        out = eng.step([StepEntry(s, [r[n + k]], [0]) for s, r, n in zip(slots, reqs, cut)])
+        for i in range(len(reqs)):
+            got[i].append(out[i:i + 1])
+    assert band.ok_all([(torch.cat(g).float().cpu(), r) for g, r in zip(got, refs)])
+
+
 def test_command_line_and_trace_replay(tmp_path):
     """``python -m rbitnet_b200 random`` makes a model of the design from its config.json; ``generate --temperature 0``
     prints the plain model's greedy ids; ``bin/trace_run`` replays a schedule of two unequal requests on the same folder."""
