@@ -336,7 +336,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 #pragma unroll
         for (int c = 0; c < HK; ++c) {
           float e, rc;
-          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(fminf(sv[c] * cap_a, 126.0f)));
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(sv[c] * cap_a));       // +inf for a large score: 1 / inf = 0
           asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(1.0f + e));
           sv[c] = fmaf(-2.0f * cap_b, rc, cap_b);
         }
