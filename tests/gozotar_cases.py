@@ -110,6 +110,29 @@ def first_tokens(make_engine, name, band):
     assert band.ok_all(pairs)
 
 
+def random_configuration(make_engine, seed, band, n=100):
+    """A configuration drawn from ``seed``: whole, the last tokens one by one, and two unequal requests together."""
+    from gozotar_tiny import random_config
+    cfg = random_config(seed)
+    tensors = make_tensors(cfg, seed=seed, spread=band.spread)
+    toks = tokens_for(cfg, n, seed)
+    ref = reference(cfg, tensors, toks)
+    eng = make_engine(cfg, tensors)
+    assert band.ok(run_cut(eng, toks, []), ref), cfg
+    assert band.ok(run_cut(eng, toks, [70] + list(range(90, n))), ref), cfg
+    other = tokens_for(cfg, 31, seed + 1)
+    slots = [eng.new_sequence(), eng.new_sequence()]
+    out = eng.step([StepEntry(slots[0], toks[:66], list(range(66))), StepEntry(slots[1], other[:29], list(range(29)))])
+    got = [[out[:66]], [out[66:]]]
+    for k in range(2):
+        out = eng.step([StepEntry(slots[0], [toks[66 + k]], [0]), StepEntry(slots[1], [other[29 + k]], [0])])
+        got[0].append(out[:1])
+        got[1].append(out[1:])
+    for s_ in slots:
+        eng.end_sequence(s_)
+    assert band.ok_all([(torch.cat(got[0]).float().cpu(), ref[:68]), (torch.cat(got[1]).float().cpu(), reference(cfg, tensors, other))]), cfg
+
+
 def retention_only():
     """Retention beside an attention branch that is switched off: what a far token does to the last logits went through
     the memory."""

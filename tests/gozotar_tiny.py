@@ -90,6 +90,48 @@ CFG_D = model(50, 36, [
 CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D}
 
 
+def random_config(seed):
+    """A configuration whose every size, option and layer order is drawn from ``seed``."""
+    import random
+    r = random.Random(seed)
+    pick = r.choice
+    width = pick([48, 64, 96, 128, 192, 256])
+    mix_kv, mix_vdim = pick([1, 2, 4]), pick([8, 16, 24, 32, 64])
+
+    def ff():
+        return pick([None, 32, 72, 128, 256])
+
+    def rotary(dim, stretched=False):
+        dims = pick([d for d in (2, 4, 8, 16, 32, 64, 128) if d <= dim])
+        sc = (pick([2.0, 4.0, 8.0]), 1.0, pick([2.0, 4.0]), pick([16, 64, 256])) if stretched and r.random() < 0.5 else None
+        return rot(pick([50.0, 1000.0, 10000.0, 500000.0]), dims, sc)
+
+    def latent():
+        dim, rd = pick([8, 16, 32, 64]), pick([2, 4, 8, 16, 32])
+        return latent_layer(pick([1, 2, 4, 8]), dim, rd, pick([8, 16, 32, 64]), pick([8, 24, 48, 96, 112]), (dim + rd) ** -0.5,
+                            base=pick([100.0, 10000.0, 1000000.0]), ff=ff())
+
+    def attention():
+        mixes = r.random() < 0.6
+        kv = mix_kv if mixes else pick([1, 2, 3])
+        dim = pick([8, 16, 32, 64, 128])
+        vdim = mix_vdim if mixes else pick([8, 16, 40, 64])
+        return attention_layer(kv * pick([1, 2, 3, 4]), kv, dim, vdim, dim ** -0.5, rotary(dim, True),
+                               pick([None, 5.0, 30.0]), mixes, ff=ff())
+
+    def parallel():
+        kv, dim = pick([1, 2, 3]), pick([8, 16, 32, 64])
+        heads = pick([1, 2, 3, 4])
+        rd = pick([8, 16, 32, 64])
+        return parallel_layer((kv * pick([1, 2, 3]), kv, dim, dim ** -0.5 * pick([1.0, 1.5]), pick([1, 2, 3, 4]), rotary(dim)),
+                              (heads, rd, pick([8, 16, 32, 64]), [pick([0.5, 0.9, 0.97, 0.99, 0.999, 1.0]) for _ in range(heads)],
+                               rotary(rd)), pick([0.3, 0.6, 1.0]), pick([0.25, 0.5, 1.0]), ff=ff())
+    layers = [pick([latent, attention, parallel])() for _ in range(r.randint(2, 5))]
+    return model(pick([64, 100, 257]), width, layers,
+                 bigram=(pick([13, 251, 1021]), pick([1, 31, 127, 40009]), pick([1, 7, 30011])) if r.random() < 0.7 else None,
+                 side=pick([3, 8, 16, 24]) if r.random() < 0.7 else None, eps=pick([1e-5, 1e-6]))
+
+
 def spec_of(cfg_dict):
     cfg = config_from_dict(cfg_dict)
     return get_architecture(cfg.architecture).build_spec(cfg)

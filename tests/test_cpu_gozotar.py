@@ -34,6 +34,11 @@ def test_prefill_against_decoding(name):
     cases.prefill_against_decoding(make_engine, name, BAND, n=30, prompt=13)
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3, 4])
+def test_random_configurations(seed):
+    cases.random_configuration(make_engine, seed, BAND, n=100)
+
+
 def test_portions():
     cases.portions(make_engine, "A", BAND, n=132)
 

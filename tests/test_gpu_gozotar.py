@@ -47,6 +47,12 @@ def test_prefill_against_decoding(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("seed", list(range(1, 17)))
+def test_random_configurations(seed, dtype):
+    cases.random_configuration(engine_maker(dtype), seed, BAND[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "C"])
 def test_portions(name, dtype):
     cases.portions(engine_maker(dtype), name, BAND[dtype])
